@@ -1,0 +1,265 @@
+"""ctypes binding of the CPU oracle (``oracle/ml2_oracle.c``).
+
+Test infrastructure: imported by ``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline
+legs of ``bench.py`` only. The product package never imports it.
+
+All arrays are numpy: fp16 as ``np.float16``, packed words as ``np.uint32``.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libml2oracle.so")
+REF_DIR = os.path.join(_HERE, "_ref")
+
+
+def build(force=False):
+    """Compiles the C oracle with gcc (and the reference's CUDA kernels when the checkout exists)."""
+    src = os.path.join(_HERE, "ml2_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE])
+    return _LIB_PATH
+
+
+def build_ref(reference_root="/root/reference", force=False):
+    """Compiles the reference's own .cu files (in place, outputs into oracle/_ref/) if the checkout is there."""
+    if not os.path.isdir(os.path.join(reference_root, "native")):
+        return False
+    if force or not os.path.exists(os.path.join(REF_DIR, "mat_vec_kernel.cubin")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + reference_root])
+    return True
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(_LIB_PATH)
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _f16(a):
+    a = np.ascontiguousarray(a, dtype=np.float16)
+    return a
+
+
+def _u32(a):
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def set_threads(n):
+    lib().orc_set_threads(ctypes.c_int(int(n)))
+
+
+def ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def qweight_sizes(rows):
+    """(weightsSize, zerosSize, scalesSize) per output, src/QKVMatVec.cs:22-24."""
+    scales = ceil_div(rows, 128)
+    return ceil_div(rows, 32) * 4, ceil_div(scales, 8), scales
+
+
+def unpack_flat(weight, zeros, scales):
+    weight, zeros, scales = _u32(weight), _u32(zeros), _f16(scales)
+    out = np.empty(weight.size * 8, dtype=np.float16)
+    lib().orc_unpack_flat(_p(weight), _p(zeros), _p(scales), ctypes.c_int(weight.size), _p(out))
+    return out
+
+
+def pack_flat(data, scales, zeros_unpacked):
+    data = _f16(data)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    zeros_unpacked = _u32(zeros_unpacked)
+    n_scales = scales.size
+    assert data.size == n_scales * 128 and zeros_unpacked.size == n_scales
+    weight = np.zeros(data.size // 8, dtype=np.uint32)
+    zeros = np.zeros(max(n_scales // 8, 1), dtype=np.uint32)
+    scales_out = np.zeros(n_scales, dtype=np.float16)
+    lib().orc_pack_flat(_p(data), _p(scales), _p(zeros_unpacked), ctypes.c_int(n_scales), _p(weight), _p(zeros),
+                        _p(scales_out))
+    return weight, zeros, scales_out
+
+
+def unpack_rows(w, z, s, rows, cols):
+    w, z, s = _u32(w), _u32(z), _f16(s)
+    out = np.empty((cols, rows), dtype=np.float16)
+    lib().orc_unpack_rows(_p(w), _p(z), _p(s), ctypes.c_int(rows), ctypes.c_int(cols), _p(out))
+    return out
+
+
+def matvec_int4_f32(x, w, z, s, rows, cols, mode=0):
+    x, w, z, s = _f16(x), _u32(w), _u32(z), _f16(s)
+    out = np.empty(cols, dtype=np.float32)
+    lib().orc_matvec_int4_f32(_p(out), _p(x), _p(w), _p(z), _p(s), ctypes.c_int(rows), ctypes.c_int(cols),
+                              ctypes.c_int(mode))
+    return out
+
+
+def matvec_residual_int4(res, x, w, z, s, rows, cols, mode=0):
+    out = _f16(res).copy()
+    x, w, z, s = _f16(x), _u32(w), _u32(z), _f16(s)
+    lib().orc_matvec_residual_int4(_p(out), _p(x), _p(w), _p(z), _p(s), ctypes.c_int(rows), ctypes.c_int(cols),
+                                   ctypes.c_int(mode))
+    return out
+
+
+def qkv_matvec_int4(x, q, k, v, rows, cols, mode=0):
+    """q, k, v are (w, z, s) triples; returns the three fp16 outputs."""
+    x = _f16(x)
+    outs = [np.empty(cols, dtype=np.float16) for _ in range(3)]
+    trip = []
+    keep = []
+    for w, z, s in (q, k, v):
+        a = (_u32(w), _u32(z), _f16(s))
+        keep.append(a)
+        trip += [_p(a[0]), _p(a[1]), _p(a[2])]
+    lib().orc_qkv_matvec_int4(_p(outs[0]), _p(outs[1]), _p(outs[2]), _p(x), *trip, ctypes.c_int(rows),
+                              ctypes.c_int(cols), ctypes.c_int(mode))
+    return outs
+
+
+def matvec_swiglu_int4(x, g, u, rows, cols, mode=0):
+    x = _f16(x)
+    out = np.empty(cols, dtype=np.float16)
+    ga = (_u32(g[0]), _u32(g[1]), _f16(g[2]))
+    ua = (_u32(u[0]), _u32(u[1]), _f16(u[2]))
+    lib().orc_matvec_swiglu_int4(_p(out), _p(x), _p(ga[0]), _p(ga[1]), _p(ga[2]), _p(ua[0]), _p(ua[1]), _p(ua[2]),
+                                 ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(mode))
+    return out
+
+
+def matvec_f16(x, w, rows, cols):
+    x, w = _f16(x), _f16(w)
+    out = np.empty(cols, dtype=np.float16)
+    lib().orc_matvec_f16(_p(out), _p(x), _p(w), ctypes.c_int(rows), ctypes.c_int(cols))
+    return out
+
+
+def attn_scores(q, k, dim, n_heads, n_kv_heads, seq_len):
+    q, k = _f16(q), _f16(k)
+    att = np.empty(n_heads * seq_len, dtype=np.float16)
+    lib().orc_attn_scores(_p(att), _p(q), _p(k), ctypes.c_int(dim), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+                          ctypes.c_int(seq_len))
+    return att
+
+
+def softmax(att, n_heads, size):
+    out = _f16(att).copy()
+    lib().orc_softmax(_p(out), ctypes.c_int(n_heads), ctypes.c_int(size))
+    return out
+
+
+def attn_values(att, v, dim, n_heads, n_kv_heads, seq_len):
+    att, v = _f16(att), _f16(v)
+    out = np.empty(dim, dtype=np.float16)
+    lib().orc_attn_values(_p(out), _p(att), _p(v), ctypes.c_int(dim), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+                          ctypes.c_int(seq_len))
+    return out
+
+
+def rmsnorm(x, gamma, eps=1e-5, fp16_square=False):
+    x, gamma = _f16(x), _f16(gamma)
+    out = np.empty_like(x)
+    lib().orc_rmsnorm(_p(out), _p(x), _p(gamma), ctypes.c_int(x.size), ctypes.c_float(eps),
+                      ctypes.c_int(1 if fp16_square else 0))
+    return out
+
+
+def rope(q, k_row, dim, n_heads, n_kv_heads, pos, theta=10000.0):
+    q, k_row = _f16(q).copy(), _f16(k_row).copy()
+    lib().orc_rope(_p(q), _p(k_row), ctypes.c_int(dim), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+                   ctypes.c_int(pos), ctypes.c_float(theta))
+    return q, k_row
+
+
+def argmax(logits):
+    logits = _f16(logits)
+    f = lib().orc_argmax
+    f.restype = ctypes.c_int
+    return int(f(_p(logits), ctypes.c_int(logits.size)))
+
+
+class _QW(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("z", ctypes.c_void_p), ("s", ctypes.c_void_p)]
+
+
+class _Config(ctypes.Structure):
+    _fields_ = [("dim", ctypes.c_int), ("hidden_dim", ctypes.c_int), ("n_layers", ctypes.c_int),
+                ("n_heads", ctypes.c_int), ("n_kv_heads", ctypes.c_int), ("vocab_size", ctypes.c_int),
+                ("seq_len", ctypes.c_int), ("rope_theta", ctypes.c_float)]
+
+
+class _Layer(ctypes.Structure):
+    _fields_ = [(n, _QW) for n in ("q", "k", "v", "o", "gate", "up", "down")] + [("rms_att", ctypes.c_void_p),
+                                                                                 ("rms_ffn", ctypes.c_void_p)]
+
+
+class _Model(ctypes.Structure):
+    _fields_ = [("cfg", _Config), ("embed", ctypes.c_void_p), ("classifier", ctypes.c_void_p),
+                ("rms_final", ctypes.c_void_p), ("layers", ctypes.c_void_p)] + \
+               [(n, ctypes.c_void_p) for n in ("x", "xb", "h", "q", "att", "logits", "key_cache", "value_cache")] + \
+               [("eps", ctypes.c_float), ("mode", ctypes.c_int)]
+
+
+class CpuModel:
+    """Whole-model CPU forward, composed like Transformer.Forward (src/Transformer.cs:158-190).
+
+    ``weights`` is a dict: embed, classifier, rms_final (fp16 arrays) and ``layers``: list of dicts with
+    q,k,v,o,gate,up,down -> (w,z,s) triples and rms_att, rms_ffn.
+    """
+
+    def __init__(self, cfg, weights, mode=1, eps=1e-5):
+        self.cfg = dict(cfg)
+        self._keep = []
+        c = self.cfg
+        kv_dim = c["dim"] * c["n_kv_heads"] // c["n_heads"]
+
+        def hold(a, dt):
+            a = np.ascontiguousarray(a, dtype=dt)
+            self._keep.append(a)
+            return a.ctypes.data
+
+        layers = (_Layer * c["n_layers"])()
+        for i, lw in enumerate(weights["layers"]):
+            for n in ("q", "k", "v", "o", "gate", "up", "down"):
+                w, z, s = lw[n]
+                setattr(layers[i], n, _QW(hold(w, np.uint32), hold(z, np.uint32), hold(s, np.float16)))
+            layers[i].rms_att = hold(lw["rms_att"], np.float16)
+            layers[i].rms_ffn = hold(lw["rms_ffn"], np.float16)
+        self._layers = layers
+        self.x = np.zeros(c["dim"], np.float16)
+        self.xb = np.zeros(c["dim"], np.float16)
+        self.h = np.zeros(c["hidden_dim"], np.float16)
+        self.q = np.zeros(c["dim"], np.float16)
+        self.att = np.zeros(c["n_heads"] * c["seq_len"], np.float16)
+        self.logits = np.zeros(c["vocab_size"], np.float16)
+        self.key_cache = np.zeros(c["n_layers"] * c["seq_len"] * kv_dim, np.float16)
+        self.value_cache = np.zeros_like(self.key_cache)
+        m = _Model()
+        m.cfg = _Config(c["dim"], c["hidden_dim"], c["n_layers"], c["n_heads"], c["n_kv_heads"], c["vocab_size"],
+                        c["seq_len"], c.get("rope_theta", 10000.0))
+        m.embed = hold(weights["embed"], np.float16)
+        m.classifier = hold(weights["classifier"], np.float16)
+        m.rms_final = hold(weights["rms_final"], np.float16)
+        m.layers = ctypes.addressof(layers)
+        for n in ("x", "xb", "h", "q", "att", "logits", "key_cache", "value_cache"):
+            setattr(m, n, getattr(self, n).ctypes.data)
+        m.eps = eps
+        m.mode = mode
+        self._m = m
+
+    def forward(self, token, pos):
+        lib().orc_forward(ctypes.byref(self._m), ctypes.c_int(int(token)), ctypes.c_int(int(pos)))
+        return self.logits.copy()
