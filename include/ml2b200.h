@@ -1,0 +1,153 @@
+/*
+ * ml2b200 - C ABI of the B200 (sm_100a) decode hot path for ManagedLlama2.
+ *
+ * Two levels, both plain C (pointers and sizes only):
+ *
+ *  1. Operator level: one entry point per `Module.Forward` of the reference's C# operator classes
+ *     (the src/ directory of GilesBathgate/ManagedLlama2). Arguments keep the reference's meaning: raw device
+ *     pointers, `rows` = d_in, `cols` = d_out, offsets into the KV cache already applied by the
+ *     caller (as `OffsetPointer` does, src/Extensions.cs:20-21). Launch geometry and the derived
+ *     sizes (`scalesSize`, `weightsSize`, `zerosSize`, src/QKVMatVec.cs:22-24) are computed inside.
+ *     Each C# subclass body becomes a single P/Invoke.
+ *
+ *  2. Model level: the per-token operator sequence of `Transformer.Forward`
+ *     (src/Transformer.cs:158-190) as five fused kernels per layer inside one CUDA graph, with
+ *     optional tensor parallelism (one process per GPU, NCCL).
+ *
+ * Every function returns 0 on success or a negative ML2_E_* code; `ml2_last_error()` gives the text
+ * for the calling thread. Nothing throws, nothing traps the device, no call falls back to the CPU.
+ * Buffers are owned by the caller unless stated; kernels only borrow them for the launch.
+ * All launches go to the context's stream (default: the legacy NULL stream, as the reference's
+ * `Module` uses, src/Module.cs:13).
+ */
+#ifndef ML2B200_H
+#define ML2B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library itself is built with -fvisibility=hidden */
+#endif
+
+#define ML2_OK 0
+#define ML2_E_INVALID (-1)   /* bad size, null or misaligned pointer, unsupported shape */
+#define ML2_E_CUDA (-2)      /* a CUDA runtime call failed; text in ml2_last_error() */
+#define ML2_E_STATE (-3)     /* call made in the wrong state (e.g. forward before bind) */
+#define ML2_E_DEVICE (-4)    /* a kernel's bounded wait ran out; status word in ml2_ctx_status() */
+#define ML2_E_NCCL (-5)      /* an NCCL call failed */
+
+typedef struct ml2_ctx ml2_ctx;
+typedef struct ml2_model ml2_model;
+
+/* Same eight fields, order and 32-byte layout as `Config` (src/Config.cs:6-17). */
+typedef struct ml2_config {
+    int32_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+    float rope_theta;
+} ml2_config;
+
+/* The three device arrays of a `QWeight` (src/QWeight.cs:5-10). */
+typedef struct ml2_qweight {
+    const uint32_t* weight; /* [cols][ceil(rows/32)*4]  8 nibbles per word, LSB first */
+    const uint32_t* zeros;  /* [cols][ceil(ceil(rows/128)/8)] 8 zero points per word */
+    const void* scales;     /* fp16 [cols][ceil(rows/128)] */
+} ml2_qweight;
+
+const char* ml2_last_error(void);
+int ml2_version(void);
+
+/* ---- context ---------------------------------------------------------------------------- */
+/* Replaces `new CudaContext(deviceID)` + per-Module PTX loading (src/Transformer.cs:48-49,
+ * src/Module.cs:15-19): binds the calling thread's primary context of `device`. */
+int ml2_ctx_create(int device, ml2_ctx** out);
+int ml2_ctx_destroy(ml2_ctx* ctx);
+int ml2_ctx_set_stream(ml2_ctx* ctx, void* cuda_stream);
+/* Programmatic dependent launch between consecutive operator calls (default off at this level:
+ * the reference's semantics are plain stream order). */
+int ml2_ctx_set_pdl(ml2_ctx* ctx, int enabled);
+int ml2_ctx_synchronize(ml2_ctx* ctx);
+/* Reads and clears the device error word written when a kernel's bounded wait expired. */
+int ml2_ctx_status(ml2_ctx* ctx, unsigned* error, unsigned* detail);
+/* Number of kernels this library has launched through `ctx` so far. */
+long long ml2_ctx_launch_count(ml2_ctx* ctx);
+
+/* ---- operator level: int4 (AWQ, group 128) mat-vec family --------------------------------- */
+/* MatVecResidual.Forward (src/MatVecResidual.cs:15-23; mat_vec_residual_int4_kernel,
+ * native/mat_vec_kernel.cu:144-164): inout[c] = half(float(inout[c]) + sum_r W[c][r]*in[r]).
+ * `in` must not alias `inout`. */
+int ml2_matvec_residual_int4(ml2_ctx* ctx, void* inout, const void* in, const ml2_qweight* w, int rows, int cols);
+/* QKVMatVec.Forward (src/QKVMatVec.cs:19-30; qkv_mat_vec_kernel, native/mat_vec_kernel.cu:179-203).
+ * q_out/k_out/v_out are the final destinations (cache row offset already applied). */
+int ml2_qkv_matvec_int4(ml2_ctx* ctx, void* q_out, void* k_out, void* v_out, const void* in, const ml2_qweight* q,
+                        const ml2_qweight* k, const ml2_qweight* v, int rows, int cols);
+/* MatVecSwiGLU.Forward (src/MatVecSwiGLU.cs:15-23; mat_vec_swiglu_kernel,
+ * native/mat_vec_kernel.cu:206-234): out[c] = half(silu(Wg.in)[c] * (Wu.in)[c]). */
+int ml2_matvec_swiglu_int4(ml2_ctx* ctx, void* out, const void* in, const ml2_qweight* gate, const ml2_qweight* up,
+                           int rows, int cols);
+/* Plain int4 mat-vec with fp16 store (device function mat_vec_int4, native/mat_vec_kernel.cu:166-177). */
+int ml2_matvec_int4(ml2_ctx* ctx, void* out, const void* in, const ml2_qweight* w, int rows, int cols);
+/* MatVec.Forward (src/MatVec.cs:15-16; mat_vec_kernel, native/mat_vec_kernel.cu:14-49): fp16
+ * matrix [cols][rows], out[c] = half(sum_r M[c][r]*in[r]). */
+int ml2_matvec_f16(ml2_ctx* ctx, void* out, const void* in, const void* matrix, int rows, int cols);
+/* Device-side HostQWeight.Unpack (src/QWeight.cs:29-54) per output row: out fp16 [cols][rows] =
+ * half((nibble - zero) * scale). Used for the bit-exact layout check. */
+int ml2_dequant_int4(ml2_ctx* ctx, void* out, const ml2_qweight* w, int rows, int cols);
+
+/* ---- operator level: attention products and the small operators --------------------------- */
+/* MatVecStrided.Forward (src/MatVecStrided.cs:16-17; mat_vec_strided_kernel,
+ * native/mat_vec_kernel.cu:51-81): att[h*seq + t] = half(scale * q_h . K[t][h]), K row stride `dim`.
+ * `key` already points at the layer's first cache row. */
+int ml2_matvec_strided(ml2_ctx* ctx, void* attention, const void* query, const void* key, int head_size, int dim,
+                       int n_heads, int seq_length, float scale);
+/* Softmax.Forward (src/Softmax.cs:14; softmax_kernel, native/softmax_kernel.cu:10-52): in place,
+ * one row of `seq_length` per head. No 8192 cap. */
+int ml2_softmax(ml2_ctx* ctx, void* attention, int n_heads, int seq_length);
+/* VecMat.Forward (src/VecMat.cs:17-18; vec_mat_kernel, native/vec_mat_kernel.cu:8-48):
+ * out[h*hs + d] = half(sum_t att[h*seq + t] * V[t][h][d]). */
+int ml2_vecmat(ml2_ctx* ctx, void* out, const void* value, const void* attention, int head_size, int dim, int n_heads,
+               int seq_length);
+/* RMSNorm.Forward (src/RMSNorm.cs:14; rmsnorm_kernel, native/rmsnorm_kernel.cu:8-42). out may alias in. */
+int ml2_rmsnorm(ml2_ctx* ctx, void* out, const void* in, const void* weights, int size, float eps);
+/* RoPERotation.Forward (src/RoPERotation.cs:19-24; rope_kernel, native/rope_kernel.cu:3-31):
+ * rotates q and the key row `key` (offset already applied) in place. */
+int ml2_rope(ml2_ctx* ctx, void* query, void* key, int n_heads, int n_kv_heads, int head_size, int pos, float theta);
+/* Embedding.Forward (src/Embedding.cs:14; embedding_kernel, native/embedding_kernel.cu:3-17). */
+int ml2_embedding(ml2_ctx* ctx, void* out, const void* table, int size, const int* tokens, int pos);
+/* Argmax.Forward (src/Argmax.cs:14; argmax_kernel, native/argmax_kernel.cu:8-46): tokens[next_pos] =
+ * argmax(logits) when write_token != 0. Ties resolve to the LOWEST index (the reference's kernel
+ * leaves ties to a race, :32-36; its CPU test expects the first maximum, test/ArgmaxTests.cs:33-46). */
+int ml2_argmax(ml2_ctx* ctx, const void* logits, int vocab_size, int* tokens, int next_pos, int write_token);
+
+/* ---- host-buffer convenience (the same operators with the copies inside the call) ---------- */
+/* Copies `in`/`inout` (host fp16) to scratch owned by the context, runs ml2_matvec_residual_int4 on
+ * device-resident weights, copies the result back and synchronises. */
+int ml2_matvec_residual_int4_host(ml2_ctx* ctx, void* inout_host, const void* in_host, const ml2_qweight* w_dev,
+                                  int rows, int cols);
+
+/* ---- synthetic tensors (counter-based, identical on host and device) ----------------------- */
+/* Fills the window [col0, col0+ncols) x groups [g0, g0+ngroups) of a logical rows_full-wide QWeight
+ * in QWeight layout with rows = ngroups*128 (or the ragged tail): nibbles and zero points uniform in
+ * [0,15], scales half(0.001 + u*0.019). `tensor_id` separates tensors; values depend only on
+ * (seed, tensor_id, logical coordinates), so a shard equals the slice of the full tensor. */
+int ml2_synth_qweight(ml2_ctx* ctx, uint32_t* weight, uint32_t* zeros, void* scales, int rows_full, int col0, int ncols,
+                      int g0, int ngroups, uint64_t seed, uint32_t tensor_id);
+/* fp16 ~ N(0, sigma^2) (Irwin-Hall of integer fields: exact, no libm) for rows [row0,row0+nrows) of a
+ * logical [*, width] tensor. */
+int ml2_synth_normal_f16(ml2_ctx* ctx, void* out, long long row0, long long nrows, int width, float sigma, uint64_t seed,
+                         uint32_t tensor_id);
+/* Host versions (for the oracle side of parity tests). */
+int ml2_synth_qweight_host(uint32_t* weight, uint32_t* zeros, void* scales, int rows_full, int col0, int ncols, int g0,
+                           int ngroups, uint64_t seed, uint32_t tensor_id);
+int ml2_synth_normal_f16_host(void* out, long long row0, long long nrows, int width, float sigma, uint64_t seed,
+                              uint32_t tensor_id);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ML2B200_H */

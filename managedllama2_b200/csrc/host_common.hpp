@@ -1,0 +1,40 @@
+// Host-side types shared by the C-ABI translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace ml2 {
+
+struct Ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    bool pdl = false;
+    DeviceStatus* status_dev = nullptr;
+    void* scratch = nullptr;          // host-buffer entry points stage their vectors here
+    size_t scratch_bytes = 0;
+    long long launches = 0;
+};
+
+struct MatVecPlan {
+    int wsize, zsize, ssize, units;
+    int kw, mw, rw, nstage;
+    int chunk_bytes, woff_z, woff_s;
+    int smem_bytes, ntiles, grid, threads;
+};
+
+enum class Fmt : int;
+enum class Epi : int;
+enum class Pro : int;
+struct MatVecParams;
+
+int fail(int code, const char* fmt, ...);
+int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, MatVecPlan* pl);
+int launch_matvec(Ctx* ctx, Fmt fmt, Epi epi, Pro pro, const MatVecPlan& pl, MatVecParams prm, bool pdl);
+
+}  // namespace ml2
