@@ -65,7 +65,7 @@ int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, 
     int mw = paired ? 2 : 1;
     while (p.kw * mw < 8 && mw * p.rw < 16) mw += paired ? 2 : 1;
     mw = env_int("ML2_MV_MW", mw);
-    if (mw < 1 || mw * p.rw > kMaxR || (paired && (mw & 1)) || (p.kw * mw + 1) * 32 > 1024)
+    if (mw < 1 || mw * p.rw > kMaxR || (paired && (mw & 1)) || (p.kw * mw + 2) * 32 > 1024)
         return fail(ML2_E_INVALID, "mat-vec plan: mw=%d invalid for kw=%d rw=%d", mw, p.kw, p.rw);
     p.mw = mw;
 
@@ -77,7 +77,7 @@ int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, 
 
     const int smem_budget = env_int("ML2_MV_SMEM_KB", 96) * 1024;
     int ctas = env_int("ML2_MV_CTAS", 0);
-    const int threads = (p.kw * p.mw + 1) * 32;
+    const int threads = (p.kw * p.mw + 2) * 32;  // consumers + producer + finalizer
     if (ctas <= 0) {
         ctas = 1;
         // small CTAs: co-schedule several per SM while the ring of each keeps >= 3 stages
@@ -119,15 +119,24 @@ static cudaError_t launch_rw(const Ctx* ctx, const MatVecPlan& pl, const MatVecP
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
+    // the opt-in to large dynamic shared memory is per function and per device: once is enough
+    static bool attr_done[2][16] = {};
+    const int dev = ctx->device & 15;
     if (pl.rw == 4) {
         auto k = stream_matvec_kernel<F, E, P, 4>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
+        if (!attr_done[0][dev]) {
+            e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            attr_done[0][dev] = true;
+        }
         return cudaLaunchKernelEx(&cfg, k, prm);
     }
     auto k = stream_matvec_kernel<F, E, P, 8>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return e;
+    if (!attr_done[1][dev]) {
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_done[1][dev] = true;
+    }
     return cudaLaunchKernelEx(&cfg, k, prm);
 }
 
@@ -137,6 +146,7 @@ int launch_matvec(Ctx* ctx, Fmt fmt, Epi epi, Pro pro, const MatVecPlan& pl, Mat
     prm.kw = pl.kw; prm.mw = pl.mw; prm.nstage = pl.nstage; prm.chunk_bytes = pl.chunk_bytes;
     prm.woff_z = pl.woff_z; prm.woff_s = pl.woff_s; prm.ntiles = pl.ntiles;
     prm.status = ctx->status_dev;
+    prm.debug = env_int("ML2_MV_DEBUG", 0);
     cudaError_t e = cudaErrorInvalidValue;
 #define ML2_CASE(F_, E_, P_) \
     if (fmt == F_ && epi == E_ && pro == P_) e = launch_rw<F_, E_, P_>(ctx, pl, prm, pdl);

@@ -62,6 +62,7 @@ struct MatVecParams {
     int woff_z, woff_s;        // byte offsets of the zeros / scales sub-regions inside a chunk
     int ntiles;                // stage-tiles in the whole problem
     int head_size;
+    int debug;                 // bit 0: consumers skip the arithmetic (pipeline probe)
 };
 
 struct Chunk {
@@ -204,22 +205,42 @@ __device__ __forceinline__ void load_input(const MatVecParams& p, int e0, bool f
 }
 
 constexpr int kMaxKW = 32;   // d_in up to 32768 (int4) / 8192 (fp16)
-constexpr int kMaxR = 32;    // rows per stage
+constexpr int kMaxR = 16;    // rows per stage
+constexpr int kMaxStages = 8;
+constexpr int kRedSlots = 8; // tiles whose k-warp partials may be waiting for the finalizer
+
+// Bounded wait shared by all roles: gives up when another role already flagged an abort, or when its own
+// limit runs out (then flags the abort and records where). The kernel always runs to its end.
+__device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile unsigned int* abort_flag,
+                                              DeviceStatus* status, unsigned int code, int tile)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((i & 1023u) == 1023u && *abort_flag) return;
+    }
+    *abort_flag = 1;
+    if (status) {
+        atomicExch(&status->error, code);
+        status->detail = (unsigned int)tile;
+    }
+}
 
 template <Fmt F, Epi E, Pro P, int RW>
 __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecParams p)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[8];
-    __shared__ __align__(8) uint64_t empty_bar[8];
-    __shared__ float s_red[2][kMaxKW][kMaxR];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];    // producer -> consumers: stage landed
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];   // consumers -> producer: stage may be refilled
+    __shared__ __align__(8) uint64_t done_bar[kRedSlots];     // consumers -> finalizer: partials of a tile complete
+    __shared__ __align__(8) uint64_t free_bar[kRedSlots];     // finalizer -> consumers: partial slot may be reused
+    __shared__ float s_red[kRedSlots][kMaxKW][kMaxR];
     __shared__ float s_part[kMaxKW];
     __shared__ unsigned int s_abort;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int ncw = p.kw * p.mw;      // consumer warps; warp `ncw` is the producer
+    const int ncw = p.kw * p.mw;      // consumer warps 0..ncw-1; warp ncw = producer; warp ncw+1 = finalizer
     const int ncons = ncw * 32;
     const int stage_bytes = p.chunk_bytes * p.mw;
 
@@ -227,6 +248,10 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
         for (int s = 0; s < p.nstage; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], ncw);
+        }
+        for (int s = 0; s < kRedSlots; ++s) {
+            mbar_init(&done_bar[s], ncw);
+            mbar_init(&free_bar[s], 1);
         }
         s_abort = 0;
         mbar_fence_init();
@@ -243,86 +268,145 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
             const int tile = blockIdx.x + i * gridDim.x;
             const int st = i % p.nstage;
             if (i >= p.nstage) {
-                bool ok = true;
-                if (lane == 0) ok = (s_abort != 0) || mbar_wait(&empty_bar[st], ((i / p.nstage) - 1) & 1);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) {
-                    if (lane == 0) {
-                        s_abort = 1;
-                        if (p.status) { atomicExch(&p.status->error, 1u); p.status->detail = tile; }
-                    }
-                }
+                if (lane == 0) wait_or_abort(&empty_bar[st], ((i / p.nstage) - 1) & 1, &s_abort, p.status, 1u, tile);
+                __syncwarp();
             }
             unsigned char* sbase = smem_raw + (size_t)st * stage_bytes;
-            // pass 1: rows whose three runs are 16-byte aligned go through the bulk-copy engine
-            uint32_t tx = 0;
-            uint32_t slow_mask = 0;
-            for (int mwi = 0; mwi < p.mw; ++mwi) {
-                const Chunk c = chunk_of<E, RW>(p, tile, mwi);
-                if (c.nrows == 0) continue;
-                const QWPtrs& q = p.mat[c.m];
-                const unsigned char* gw = reinterpret_cast<const unsigned char*>(q.w + (size_t)c.row0 * p.wsize);
-                const uint32_t bw = (uint32_t)c.nrows * p.wsize * 4u;
-                bool fast = ((reinterpret_cast<uintptr_t>(gw) | bw) & 15u) == 0;
-                const unsigned char* gz = nullptr;
-                const unsigned char* gs = nullptr;
-                uint32_t bz = 0, bs = 0;
-                if constexpr (F == Fmt::Int4) {
-                    gz = reinterpret_cast<const unsigned char*>(q.z + (size_t)c.row0 * p.zsize);
-                    gs = reinterpret_cast<const unsigned char*>(q.s + (size_t)c.row0 * p.ssize);
-                    bz = (uint32_t)c.nrows * p.zsize * 4u;
-                    bs = (uint32_t)c.nrows * p.ssize * 2u;
-                    fast = fast && (((reinterpret_cast<uintptr_t>(gz) | bz) & 15u) == 0) &&
-                           (((reinterpret_cast<uintptr_t>(gs) | bs) & 15u) == 0);
-                }
-                if (!fast) {
-                    slow_mask |= 1u << mwi;
-                    continue;
-                }
-                tx += bw + bz + bs;
+            // lane m describes chunk m (one pass, in parallel); runs that are 16-byte aligned go through the
+            // bulk-copy engine, anything else (ragged tail, odd strides) through a cooperative copy
+            Chunk c{0, 0, 0};
+            if (lane < p.mw) c = chunk_of<E, RW>(p, tile, lane);
+            const QWPtrs q = p.mat[c.m < p.nmat ? c.m : 0];
+            const uint32_t* gw = q.w + (size_t)c.row0 * p.wsize;
+            const uint32_t bw = (uint32_t)c.nrows * p.wsize * 4u;
+            bool fast = ((reinterpret_cast<uintptr_t>(gw) | bw) & 15u) == 0;
+            const uint32_t* gz = nullptr;
+            const __half* gs = nullptr;
+            uint32_t bz = 0, bs = 0;
+            if (F == Fmt::Int4 && !(p.debug & 2)) {
+                gz = q.z + (size_t)c.row0 * p.zsize;
+                gs = q.s + (size_t)c.row0 * p.ssize;
+                bz = (uint32_t)c.nrows * p.zsize * 4u;
+                bs = (uint32_t)c.nrows * p.ssize * 2u;
+                fast = fast && (((reinterpret_cast<uintptr_t>(gz) | bz) & 15u) == 0) &&
+                       (((reinterpret_cast<uintptr_t>(gs) | bs) & 15u) == 0);
             }
-            // slow chunks (ragged tail or odd strides): cooperative 2-byte copies by the whole warp
+            const bool live = c.nrows > 0;
+            uint32_t tx = (live && fast) ? (bw + bz + bs) : 0u;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
+            const uint32_t slow_mask = __ballot_sync(0xffffffffu, live && !fast);
             if (slow_mask) {
                 for (int mwi = 0; mwi < p.mw; ++mwi) {
                     if (!((slow_mask >> mwi) & 1u)) continue;
-                    const Chunk c = chunk_of<E, RW>(p, tile, mwi);
-                    const QWPtrs& q = p.mat[c.m];
+                    const Chunk cs = chunk_of<E, RW>(p, tile, mwi);
+                    const QWPtrs& qs = p.mat[cs.m];
                     unsigned char* cb = sbase + (size_t)mwi * p.chunk_bytes;
-                    const uint32_t* gw = q.w + (size_t)c.row0 * p.wsize;
+                    const uint32_t* sw = qs.w + (size_t)cs.row0 * p.wsize;
                     uint32_t* dw = reinterpret_cast<uint32_t*>(cb);
-                    for (int k = lane; k < c.nrows * p.wsize; k += 32) dw[k] = gw[k];
+                    for (int k = lane; k < cs.nrows * p.wsize; k += 32) dw[k] = sw[k];
                     if constexpr (F == Fmt::Int4) {
-                        const uint32_t* gz = q.z + (size_t)c.row0 * p.zsize;
+                        const uint32_t* sz = qs.z + (size_t)cs.row0 * p.zsize;
                         uint32_t* dz = reinterpret_cast<uint32_t*>(cb + p.woff_z);
-                        for (int k = lane; k < c.nrows * p.zsize; k += 32) dz[k] = gz[k];
-                        const __half* gs = q.s + (size_t)c.row0 * p.ssize;
+                        for (int k = lane; k < cs.nrows * p.zsize; k += 32) dz[k] = sz[k];
+                        const __half* ss = qs.s + (size_t)cs.row0 * p.ssize;
                         __half* ds = reinterpret_cast<__half*>(cb + p.woff_s);
-                        for (int k = lane; k < c.nrows * p.ssize; k += 32) ds[k] = gs[k];
+                        for (int k = lane; k < cs.nrows * p.ssize; k += 32) ds[k] = ss[k];
                     }
                 }
                 __syncwarp();
             }
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&full_bar[st], tx);
-                for (int mwi = 0; mwi < p.mw; ++mwi) {
-                    if ((slow_mask >> mwi) & 1u) continue;
-                    const Chunk c = chunk_of<E, RW>(p, tile, mwi);
-                    if (c.nrows == 0) continue;
-                    const QWPtrs& q = p.mat[c.m];
-                    unsigned char* cb = sbase + (size_t)mwi * p.chunk_bytes;
-                    bulk_g2s(cb, q.w + (size_t)c.row0 * p.wsize, (uint32_t)c.nrows * p.wsize * 4u, &full_bar[st], pol);
-                    if constexpr (F == Fmt::Int4) {
-                        bulk_g2s(cb + p.woff_z, q.z + (size_t)c.row0 * p.zsize, (uint32_t)c.nrows * p.zsize * 4u,
-                                 &full_bar[st], pol);
-                        bulk_g2s(cb + p.woff_s, q.s + (size_t)c.row0 * p.ssize, (uint32_t)c.nrows * p.ssize * 2u,
-                                 &full_bar[st], pol);
-                    }
+            if (lane == 0) mbar_arrive_expect_tx(&full_bar[st], tx);
+            __syncwarp();
+            if (live && fast) {
+                unsigned char* cb = sbase + (size_t)lane * p.chunk_bytes;
+                bulk_g2s(cb, gw, bw, &full_bar[st], pol);
+                if (F == Fmt::Int4 && !(p.debug & 2)) {
+                    bulk_g2s(cb + p.woff_z, gz, bz, &full_bar[st], pol);
+                    bulk_g2s(cb + p.woff_s, gs, bs, &full_bar[st], pol);
                 }
             }
         }
         return;
     }
-    if (warp > ncw) return;
+
+    if (warp == ncw + 1) {
+        // ---------------- finalizer warp: fixed-order sum over k-warps, then the operator's tail ------
+        pdl_wait();  // outputs (and the residual read) belong after the previous kernel
+        const int pos = (E == Epi::QKVRope) ? (p.pos_ptr ? *p.pos_ptr : p.pos_imm) : 0;
+        for (int i = 0; i < my_tiles; ++i) {
+            const int tile = blockIdx.x + i * gridDim.x;
+            const int slot = i % kRedSlots;
+            const float* red = &s_red[slot][0][0];
+            if constexpr (E == Epi::SwiGLU || E == Epi::QKVRope) {
+                const int npair = (p.mw >> 1) * RW;
+                const int pr = lane / RW, r = lane - pr * RW;
+                const bool mine = lane < npair;
+                Chunk ca{0, 0, 0}, cbk{0, 0, 0};
+                if (mine) {
+                    ca = chunk_of<E, RW>(p, tile, 2 * pr);
+                    cbk = chunk_of<E, RW>(p, tile, 2 * pr + 1);
+                }
+                float2 cs = make_float2(1.f, 0.f);
+                if (E == Epi::QKVRope && mine && r < ca.nrows && ca.m < 2)
+                    cs = p.rope_table[(size_t)pos * (p.head_size >> 1) + (ca.row0 + r) % p.head_size];
+                wait_or_abort(&done_bar[slot], (i / kRedSlots) & 1, &s_abort, p.status, 3u, tile);
+                if (mine && r < ca.nrows) {
+                    float sa = 0.f, sb = 0.f;
+                    for (int k = 0; k < p.kw; ++k) {
+                        sa += red[k * kMaxR + (2 * pr) * RW + r];
+                        sb += red[k * kMaxR + (2 * pr + 1) * RW + r];
+                    }
+                    if constexpr (E == Epi::SwiGLU) {
+                        // native/mat_vec_kernel.cu:218-222
+                        float val = sa;
+                        val *= 1.0f / (1.0f + expf(-val));
+                        val *= sb;
+                        p.out[0][ca.row0 + r] = __float2half_rn(val);
+                    } else {
+                        __half* o = p.out[ca.m];
+                        if (ca.m > 0 && p.pos_ptr) o += (long long)pos * p.kv_row_stride;
+                        if (ca.m < 2) {
+                            // fp16 store of the mat-vec result (native/mat_vec_kernel.cu:175), then RoPE on the
+                            // rounded values (native/rope_kernel.cu:15-25)
+                            const float a0 = __half2float(__float2half_rn(sa));
+                            const float b0 = __half2float(__float2half_rn(sb));
+                            o[ca.row0 + r] = __float2half_rn(a0 * cs.x - b0 * cs.y);
+                            o[cbk.row0 + r] = __float2half_rn(a0 * cs.y + b0 * cs.x);
+                        } else {
+                            o[ca.row0 + r] = __float2half_rn(sa);
+                            o[cbk.row0 + r] = __float2half_rn(sb);
+                        }
+                    }
+                }
+            } else {
+                const int nrow = p.mw * RW;
+                const int ch = lane / RW, r = lane - ch * RW;
+                Chunk c{0, 0, 0};
+                if (lane < nrow) c = chunk_of<E, RW>(p, tile, ch);
+                const bool mine = lane < nrow && r < c.nrows;
+                const int row = c.row0 + r;
+                float resid = 0.f;
+                if (E == Epi::Residual && mine) resid = __half2float(p.out[0][row]);  // issued before the wait
+                wait_or_abort(&done_bar[slot], (i / kRedSlots) & 1, &s_abort, p.status, 3u, tile);
+                if (mine) {
+                    float sum = 0.f;
+                    for (int k = 0; k < p.kw; ++k) sum += red[k * kMaxR + lane];
+                    if constexpr (E == Epi::Store) {
+                        p.out[c.m][row] = __float2half_rn(sum);
+                    } else if constexpr (E == Epi::Residual) {
+                        p.out[0][row] = __float2half_rn(sum + resid);  // native/mat_vec_kernel.cu:154-156
+                    } else {
+                        p.out_f32[row] = sum;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&free_bar[slot]);
+        }
+        return;
+    }
+    if (warp > ncw + 1) return;
 
     // ---------------- consumer warps ------------------------------------------------------------
     const int kw_id = warp % p.kw;
@@ -362,25 +446,38 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
         for (int i = 0; i < NX / 2; ++i) xp[i] = xr[i];
     }
     const int g = u >> 2;             // quantisation group of this lane's slice (Int4)
-    const int zword = g >> 3;
     const int zshift = (g & 7) * 4;
+    // lane-invariant offsets inside a chunk
+    const uint32_t chunk_base = smem_u32(smem_raw) + (uint32_t)mw_id * p.chunk_bytes;
+    const uint32_t w_off = (uint32_t)(active ? u : 0) * 16u;
+    const uint32_t z_off = p.woff_z + (uint32_t)(active ? (g >> 3) : 0) * 4u;
+    const uint32_t s_off = p.woff_s + (uint32_t)(active ? g : 0) * 2u;
+    const uint32_t w_row = (uint32_t)p.wsize * 4u, z_row = (uint32_t)p.zsize * 4u, s_row = (uint32_t)p.ssize * 2u;
+    const bool writer = (lane & (32 / RW - 1)) == 0;
+    float* red_dst = &s_red[0][kw_id][mw_id * RW + lane / (32 / RW)];  // + slot * kMaxKW * kMaxR
 
     for (int i = 0; i < my_tiles; ++i) {
-        const int tile = blockIdx.x + i * gridDim.x;
         const int st = i % p.nstage;
-        if (s_abort == 0 && !mbar_wait(&full_bar[st], (i / p.nstage) & 1)) {
-            s_abort = 1;
-            if (p.status) { atomicExch(&p.status->error, 2u); p.status->detail = tile; }
-        }
-        const unsigned char* cb = smem_raw + (size_t)st * stage_bytes + (size_t)mw_id * p.chunk_bytes;
-        const uint4* wsm = reinterpret_cast<const uint4*>(cb);
+        wait_or_abort(&full_bar[st], (i / p.nstage) & 1, &s_abort, p.status, 2u, i);
+        const uint32_t cb = chunk_base + (uint32_t)st * stage_bytes;
         float v[RW];
-        if constexpr (F == Fmt::Int4) {
-            const uint32_t* zsm = reinterpret_cast<const uint32_t*>(cb + p.woff_z);
-            const unsigned short* ssm = reinterpret_cast<const unsigned short*>(cb + p.woff_s);
+        if (p.debug & 1) {
+#pragma unroll
+            for (int r = 0; r < RW; ++r) v[r] = 0.f;
+        } else if constexpr (F == Fmt::Int4) {
             uint4 wv[RW];
 #pragma unroll
-            for (int r = 0; r < RW; ++r) wv[r] = active ? wsm[r * p.units + u] : make_uint4(0, 0, 0, 0);
+            for (int r = 0; r < RW; ++r)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(wv[r].x), "=r"(wv[r].y), "=r"(wv[r].z), "=r"(wv[r].w)
+                             : "r"(cb + w_off + r * w_row));
+            uint32_t zw[RW];
+            unsigned short sc[RW];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cb + z_off + r * z_row));
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cb + s_off + r * s_row));
+            }
             float alo[RW], ahi[RW];
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
@@ -393,20 +490,18 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
             }
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
-                float res = 0.f;
-                if (active) {
-                    const uint32_t zw = zsm[r * p.zsize + zword];
-                    const float zf = (float)((zw >> zshift) & 0xFu);
-                    const float sc = half_bits_to_float(ssm[r * p.ssize + g]);
-                    const float t = fmaf(ahi[r], 0.0625f, alo[r]);
-                    res = sc * fmaf(-zf, c1, t);
-                }
-                v[r] = res;
+                const float zf = (float)((zw[r] >> zshift) & 0xFu);
+                const float t = fmaf(ahi[r], 0.0625f, alo[r]);
+                const float res = half_bits_to_float(sc[r]) * fmaf(-zf, c1, t);
+                v[r] = active ? res : 0.f;
             }
         } else {
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
-                const uint4 wv = active ? wsm[r * p.units + u] : make_uint4(0, 0, 0, 0);
+                uint4 wv;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
+                             : "r"(cb + w_off + r * w_row));
                 float a0 = 0.f, a1 = 0.f;
                 a0 = fma_f16_f32(lo16(wv.x), lo16(xp[0]), a0);
                 a1 = fma_f16_f32(hi16(wv.x), hi16(xp[0]), a1);
@@ -416,77 +511,20 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
                 a1 = fma_f16_f32(hi16(wv.z), hi16(xp[2]), a1);
                 a0 = fma_f16_f32(lo16(wv.w), lo16(xp[3]), a0);
                 a1 = fma_f16_f32(hi16(wv.w), hi16(xp[3]), a1);
-                v[r] = a0 + a1;
+                v[r] = active ? (a0 + a1) : 0.f;
             }
         }
         // this warp is done with the stage: hand it back to the producer
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[st]);
 
+        // deposit the row sums of this warp's k-slice for the finalizer
         transpose_reduce<RW>(v, lane);
-        if ((lane & (32 / RW - 1)) == 0) s_red[i & 1][kw_id][mw_id * RW + lane / (32 / RW)] = v[0];
-        named_bar_sync(1, ncons);
-
-        // ---------------- epilogue: fixed-order sum over k-warps, then the operator's tail -----
-        const float* red = &s_red[i & 1][0][0];
-        if constexpr (E == Epi::SwiGLU || E == Epi::QKVRope) {
-            const int npair = (p.mw >> 1) * RW;
-            if (tid < npair) {
-                const int pr = tid / RW, r = tid - pr * RW;
-                const Chunk ca = chunk_of<E, RW>(p, tile, 2 * pr);
-                if (r < ca.nrows) {
-                    float sa = 0.f, sb = 0.f;
-                    for (int k = 0; k < p.kw; ++k) {
-                        sa += red[k * kMaxR + (2 * pr) * RW + r];
-                        sb += red[k * kMaxR + (2 * pr + 1) * RW + r];
-                    }
-                    if (E == Epi::SwiGLU) {
-                        // native/mat_vec_kernel.cu:218-222
-                        float val = sa;
-                        val *= 1.0f / (1.0f + expf(-val));
-                        val *= sb;
-                        p.out[0][ca.row0 + r] = __float2half_rn(val);
-                    } else {
-                        const Chunk cbk = chunk_of<E, RW>(p, tile, 2 * pr + 1);
-                        const int pos = p.pos_ptr ? *p.pos_ptr : p.pos_imm;
-                        __half* o = p.out[ca.m];
-                        if (ca.m > 0 && p.pos_ptr) o += (long long)pos * p.kv_row_stride;
-                        // fp16 store of the mat-vec result (native/mat_vec_kernel.cu:175), then RoPE on the
-                        // rounded values (native/rope_kernel.cu:15-25); v is stored as is.
-                        const float a0 = __half2float(__float2half_rn(sa));
-                        const float b0 = __half2float(__float2half_rn(sb));
-                        if (ca.m < 2) {
-                            const int half = p.head_size >> 1;
-                            const float2 cs = p.rope_table[(size_t)pos * half + (ca.row0 + r) % p.head_size];
-                            o[ca.row0 + r] = __float2half_rn(a0 * cs.x - b0 * cs.y);
-                            o[cbk.row0 + r] = __float2half_rn(a0 * cs.y + b0 * cs.x);
-                        } else {
-                            o[ca.row0 + r] = __float2half_rn(sa);
-                            o[cbk.row0 + r] = __float2half_rn(sb);
-                        }
-                    }
-                }
-            }
-        } else {
-            const int nrow = p.mw * RW;
-            if (tid < nrow) {
-                const int ch = tid / RW, r = tid - ch * RW;
-                const Chunk c = chunk_of<E, RW>(p, tile, ch);
-                if (r < c.nrows) {
-                    float sum = 0.f;
-                    for (int k = 0; k < p.kw; ++k) sum += red[k * kMaxR + tid];
-                    const int row = c.row0 + r;
-                    if (E == Epi::Store) {
-                        p.out[c.m][row] = __float2half_rn(sum);
-                    } else if (E == Epi::Residual) {
-                        // native/mat_vec_kernel.cu:154-156
-                        p.out[0][row] = __float2half_rn(sum + __half2float(p.out[0][row]));
-                    } else {
-                        p.out_f32[row] = sum;
-                    }
-                }
-            }
-        }
+        const int slot = i % kRedSlots;
+        if (i >= kRedSlots) wait_or_abort(&free_bar[slot], ((i / kRedSlots) - 1) & 1, &s_abort, p.status, 4u, i);
+        if (writer) red_dst[slot * (kMaxKW * kMaxR)] = v[0];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&done_bar[slot]);
     }
 }
 
