@@ -144,6 +144,60 @@ int ml2_synth_qweight_host(uint32_t* weight, uint32_t* zeros, void* scales, int 
 int ml2_synth_normal_f16_host(void* out, long long row0, long long nrows, int width, float sigma, uint64_t seed,
                               uint32_t tensor_id);
 
+/* ---- model level -------------------------------------------------------------------------------- */
+/* Device pointers of one layer, named as in PerLayerWeight (src/PerLayerWeight.cs:5-16). Under tensor
+ * parallelism these are the rank's shards (see ml2_model_local_shape). */
+typedef struct ml2_layer_weights {
+    ml2_qweight query, key, value, output, gate, up, down;
+    const void* rms_attention;    /* fp16 [dim] */
+    const void* rms_feed_forward; /* fp16 [dim] */
+} ml2_layer_weights;
+
+/* Device buffers of RunState (src/RunState.cs:5-25). key/value caches are [layer][seq_len][kv_dim_local]. */
+typedef struct ml2_runstate {
+    void *x, *xb, *h, *q, *logits, *key_cache, *value_cache;
+    int* tokens; /* [seq_len + 1] */
+} ml2_runstate;
+
+/* 128-byte NCCL unique id; rank 0 creates it, every rank passes the same bytes to ml2_model_create. */
+int ml2_nccl_unique_id(void* out128);
+/* Stands for the Transformer constructor (src/Transformer.cs:46-87) minus file reading: validates the
+ * config (GQA is refused like the reference does, :53-56), builds the RoPE table, joins the NCCL group
+ * when tp_size > 1 (one process per GPU). The model uses a stream of its own. */
+int ml2_model_create(ml2_ctx* ctx, const ml2_config* cfg, int tp_size, int tp_rank, const void* nccl_id128, ml2_model** out);
+int ml2_model_destroy(ml2_model* model);
+/* Shard owned by this rank: attention width (heads*128), hidden rows (whole groups of 128, starting at
+ * group hidden_group0), vocabulary rows (starting at vocab_row0). */
+int ml2_model_local_shape(ml2_model* model, int* dim_local, int* hidden_local, int* vocab_local, int* hidden_group0,
+                          int* vocab_row0);
+void ml2_tp_hidden_groups(int hidden_dim, int tp_size, int tp_rank, int* group0, int* ngroups);
+/* Borrow the caller's device arrays (TransformerWeights, src/TransformerWeights.cs:8-16). `classifier_local`
+ * holds this rank's vocabulary rows. */
+int ml2_model_bind_globals(ml2_model* model, const void* embed, const void* classifier_local, const void* rms_final);
+int ml2_model_bind_layer(ml2_model* model, int layer, const ml2_layer_weights* w);
+/* Run state: either allocated (and owned) by the library or borrowed from the caller. */
+int ml2_model_alloc_runstate(ml2_model* model);
+int ml2_model_bind_runstate(ml2_model* model, const ml2_runstate* rs);
+int ml2_model_runstate(ml2_model* model, ml2_runstate* rs);
+/* Transformer.Forward(position, nextPosition) followed by the greedy Sampler.Sample
+ * (src/Transformer.cs:158-190, src/Sampler.cs:44-47): asynchronous; tokens[next_pos] is written on the
+ * device when write_token != 0. One CUDA-graph replay per call. */
+int ml2_model_forward(ml2_model* model, int pos, int next_pos, int write_token);
+int ml2_model_synchronize(ml2_model* model);
+long long ml2_model_launches_per_token(ml2_model* model);
+int ml2_model_set_tokens(ml2_model* model, const int* tokens_host, int first, int count);
+/* Stream-ordered 4-byte host->device copy of one token id; `token_pinned_host` must stay valid until it ran. */
+int ml2_model_put_token_async(ml2_model* model, int pos, const int* token_pinned_host);
+int ml2_model_read_token(ml2_model* model, int pos, int* token_host);
+int ml2_model_read_logits(ml2_model* model, void* logits_host_f16);
+/* The CUDA stream the model launches on (for events or for ordering other work after it). */
+int ml2_model_stream(ml2_model* model, void** cuda_stream);
+/* Times each kernel kind alone over all layers (kinds: 0 qkv, 1 attention, 2 o-proj, 3 gate/up, 4 down,
+ * 5 classifier): average microseconds per launch and the algorithmic bytes one launch moves. */
+int ml2_model_profile(ml2_model* model, int iters, double* avg_us6, double* algo_bytes6);
+/* Transformer.Generate on token ids (src/Transformer.cs:89-112): HOST buffers in and out, copies inside. */
+int ml2_model_generate(ml2_model* model, const int* prompt_host, int n_prompt, int steps, int* out_tokens_host, int* n_out);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -30,9 +30,7 @@ def build(force=False, verbose=False):
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_source_mtime():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, "-shared", "-o", LIB] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-lcudart", "-lnccl"]
-    if not any(os.path.basename(s) == "model.cu" for s in srcs):
-        cmd.remove("-lnccl")
+    cmd = [nvcc, "-shared", "-o", LIB] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-lcudart", "-ldl"]
     subprocess.check_call(cmd)
     return LIB
 

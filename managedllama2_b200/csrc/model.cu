@@ -1,0 +1,782 @@
+// C ABI, model level: Transformer.Forward of the reference (src/Transformer.cs:158-190) as five fused
+// kernels per layer replayed from one CUDA graph, with optional tensor parallelism (one process per GPU).
+//
+// Per layer, single GPU:
+//   1. RMSNorm + QKV int4 mat-vec + RoPE, k/v written straight into the cache row      (reference: 3 launches)
+//   2. fused attention (scores, softmax, values)                                       (reference: 3 launches)
+//   3. o-proj int4 mat-vec + residual
+//   4. RMSNorm + gate/up int4 mat-vec + SwiGLU                                         (reference: 2 launches)
+//   5. down int4 mat-vec + residual
+// then RMSNorm + fp16 classifier and the arg-max. The position lives in device memory (StepState), so
+// one graph serves every token; only the first node's parameters are refreshed per replay.
+//
+// Tensor parallel (tp > 1): QKV / gate / up sharded by output rows, o-proj / down by input groups of
+// 128, KV cache by heads, classifier by vocabulary rows. o-proj and down produce fp32 partials that
+// are summed with ncclAllReduce before the single fp16 rounding of the residual add, so every rank
+// holds bit-identical activations.
+#include "../../include/ml2b200.h"
+
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "attention.cuh"
+#include "host_common.hpp"
+#include "small_ops.cuh"
+#include "stream_matvec.cuh"
+
+namespace ml2 {
+
+// NCCL is bound at run time, and only when tensor parallelism is used: a process that already carries an
+// NCCL (e.g. the one PyTorch ships) keeps exactly that copy; otherwise the system library is loaded.
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+static NcclApi g_nccl;
+
+static int nccl_load()
+{
+    if (g_nccl.ok) return ML2_OK;
+    const char* override_path = getenv("ML2_NCCL_LIB");
+    void* h = nullptr;
+    if (override_path && *override_path) h = dlopen(override_path, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);  // already in the process
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(ML2_E_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+#define ML2_SYM(field, name)                                                       \
+    g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(h, name));       \
+    if (!g_nccl.field) return fail(ML2_E_NCCL, "libnccl.so.2 lacks %s", name);
+    ML2_SYM(GetUniqueId, "ncclGetUniqueId")
+    ML2_SYM(CommInitRank, "ncclCommInitRank")
+    ML2_SYM(CommDestroy, "ncclCommDestroy")
+    ML2_SYM(AllReduce, "ncclAllReduce")
+    ML2_SYM(AllGather, "ncclAllGather")
+    ML2_SYM(GetErrorString, "ncclGetErrorString")
+#undef ML2_SYM
+    g_nccl.ok = true;
+    return ML2_OK;
+}
+
+struct StepState {
+    int pos;
+    int next_pos;
+    int write_token;
+    int reserved;
+};
+
+// first node of the token graph: publishes the step and gathers the embedding row
+// (native/embedding_kernel.cu:3-17)
+__global__ void begin_step_kernel(StepState* st, int pos, int next_pos, int write_token, __half* x, const __half* table, int dim,
+                                  const int* tokens)
+{
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        st->pos = pos;
+        st->next_pos = next_pos;
+        st->write_token = write_token;
+    }
+    const int token = tokens[pos];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x) x[i] = table[(size_t)token * dim + i];
+}
+
+// argmax with the step taken from device memory (native/argmax_kernel.cu:8-46; lowest index wins ties)
+__global__ void __launch_bounds__(1024) argmax_step_kernel(const __half* logits, int size, int* tokens, const StepState* st)
+{
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    pdl_wait();
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = __half2float(logits[i]);
+        if (v > best) { best = v; best_i = i; }
+    }
+    auto better = [](float a, int ai, float b, int bi) { return a > b || (a == b && ai < bi); };
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < nw ? s_val[lane] : -INFINITY;
+        best_i = lane < nw ? s_idx[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+        }
+        if (lane == 0 && st->write_token) tokens[st->next_pos] = (best_i == 0x7fffffff) ? 0 : best_i;
+    }
+}
+
+// x = half(float(x) + all-reduced partial): the residual add of the row-sharded mat-vecs
+// (rounding point of native/mat_vec_kernel.cu:154-156)
+__global__ void residual_add_f32_kernel(__half* x, const float* sum, int n)
+{
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = __float2half_rn(__half2float(x[i]) + sum[i]);
+}
+
+struct LayerW {
+    ml2_qweight q, k, v, o, gate, up, down;
+    const __half* rms_att;
+    const __half* rms_ffn;
+    bool bound = false;
+};
+
+struct Model {
+    Ctx* ctx = nullptr;
+    ml2_config cfg{};
+    int tp = 1, rank = 0;
+    // local (per-rank) shapes
+    int heads_local = 0, dim_local = 0;    // attention width owned by this rank
+    int hidden_local = 0;                   // hidden rows owned (whole groups of 128)
+    int vocab_local = 0, vocab_row0 = 0;
+    int head_size = 0;
+    float eps = 1e-5f;
+    std::vector<LayerW> layers;
+    const __half* embed = nullptr;
+    const __half* classifier = nullptr;     // local vocabulary rows
+    const __half* rms_final = nullptr;
+    // run state (src/RunState.cs:5-25); owned here unless bound by the caller
+    __half *x = nullptr, *xb = nullptr, *h = nullptr, *q = nullptr, *logits = nullptr, *att = nullptr;
+    __half *key_cache = nullptr, *value_cache = nullptr;
+    int* tokens = nullptr;
+    bool own_state = false;
+    float* partial = nullptr;               // fp32 [dim], tp > 1
+    __half* logits_local = nullptr;         // tp > 1
+    float2* rope_table = nullptr;
+    StepState* step = nullptr;
+    ncclComm_t comm = nullptr;
+    // graph
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaGraphNode_t first_node = nullptr;
+    cudaStream_t stream = nullptr;          // owned non-blocking stream used for capture and replay
+    bool use_graph = true;
+    bool use_pdl = true;
+    long long launches_per_token = 0;
+    std::vector<void*> owned;
+};
+
+#define ML2_CUDA(call)                                                                       \
+    do {                                                                                     \
+        const cudaError_t e_ = (call);                                                       \
+        if (e_ != cudaSuccess) return fail(ML2_E_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+#define ML2_NCCL(call)                                                                       \
+    do {                                                                                     \
+        const ncclResult_t r_ = (call);                                                      \
+        if (r_ != ncclSuccess) return fail(ML2_E_NCCL, "%s: %s", #call, g_nccl.GetErrorString(r_)); \
+    } while (0)
+
+static int dev_alloc(Model* m, void** p, size_t bytes)
+{
+    ML2_CUDA(cudaMalloc(p, bytes));
+    ML2_CUDA(cudaMemsetAsync(*p, 0, bytes, m->stream));
+    m->owned.push_back(*p);
+    return ML2_OK;
+}
+
+static QWPtrs qwp(const ml2_qweight& q) { return QWPtrs{q.weight, q.zeros, static_cast<const __half*>(q.scales)}; }
+
+template <typename... Args>
+static int launch_k(Model* m, const char* what, void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, bool pdl, Args... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = m->ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl && m->use_pdl) ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+    if (e != cudaSuccess) return fail(ML2_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    ++m->ctx->launches;
+    return ML2_OK;
+}
+
+// One token's worth of launches on ctx->stream (captured once, or issued eagerly).
+static int enqueue_token(Model* m, int pos, int next_pos, int write_token)
+{
+    Ctx* ctx = m->ctx;
+    const ml2_config& c = m->cfg;
+    const int dim = c.dim;
+    const bool pdl = m->use_pdl;
+    int rc;
+    const long long before = ctx->launches;
+
+    if ((rc = launch_k(m, "begin_step", begin_step_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, false, m->step, pos, next_pos,
+                       write_token, m->x, m->embed, dim, (const int*)m->tokens)))
+        return rc;
+
+    MatVecPlan pl_qkv, pl_o, pl_gu, pl_down, pl_cls;
+    if ((rc = plan_matvec(ctx, Fmt::Int4, Epi::QKVRope, dim, m->dim_local, 3, &pl_qkv))) return rc;
+    if ((rc = plan_matvec(ctx, Fmt::Int4, m->tp > 1 ? Epi::PartialF32 : Epi::Residual, m->dim_local, dim, 1, &pl_o))) return rc;
+    if ((rc = plan_matvec(ctx, Fmt::Int4, Epi::SwiGLU, dim, m->hidden_local, 2, &pl_gu))) return rc;
+    if ((rc = plan_matvec(ctx, Fmt::Int4, m->tp > 1 ? Epi::PartialF32 : Epi::Residual, m->hidden_local, dim, 1, &pl_down))) return rc;
+    if ((rc = plan_matvec(ctx, Fmt::F16, Epi::Store, dim, m->vocab_local, 1, &pl_cls))) return rc;
+
+    const size_t kv_layer = (size_t)c.seq_len * m->dim_local;
+    const int chunk_cap = std::max(ceil_div(c.seq_len, kAttnCluster), kAttnSingleCtaMax);
+
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerW& L = m->layers[l];
+        __half* kc = m->key_cache + (size_t)l * kv_layer;
+        __half* vc = m->value_cache + (size_t)l * kv_layer;
+        {   // 1. rmsnorm + qkv + rope (src/Transformer.cs:167-173)
+            MatVecParams p{};
+            p.mat[0] = qwp(L.q); p.mat[1] = qwp(L.k); p.mat[2] = qwp(L.v);
+            p.out[0] = m->q; p.out[1] = kc; p.out[2] = vc;
+            p.in = m->x; p.gamma = L.rms_att; p.eps = m->eps;
+            p.rope_table = m->rope_table; p.pos_ptr = &m->step->pos; p.kv_row_stride = m->dim_local;
+            p.rows = dim; p.cols = m->dim_local; p.nmat = 3; p.head_size = m->head_size;
+            if ((rc = launch_matvec(ctx, Fmt::Int4, Epi::QKVRope, Pro::RMSNorm, pl_qkv, p, pdl))) return rc;
+        }
+        {   // 2. attention (src/Transformer.cs:150-156)
+            AttnParams a{};
+            a.out = m->xb; a.q = m->q; a.k = kc; a.v = vc; a.pos_ptr = &m->step->pos;
+            a.n_heads = m->heads_local; a.head_size = m->head_size; a.row_stride = m->dim_local;
+            a.scale = 1.0f / sqrtf((float)m->head_size); a.chunk_cap = chunk_cap;
+            if ((rc = launch_k(m, "attention", fused_attention_kernel, dim3(m->heads_local * kAttnCluster), dim3(kAttnThreads),
+                               (size_t)chunk_cap * sizeof(float), true, a)))
+                return rc;
+        }
+        {   // 3. o-proj + residual (:177)
+            MatVecParams p{};
+            p.mat[0] = qwp(L.o); p.in = m->xb; p.rows = m->dim_local; p.cols = dim; p.nmat = 1;
+            if (m->tp > 1) {
+                p.out_f32 = m->partial;
+                if ((rc = launch_matvec(ctx, Fmt::Int4, Epi::PartialF32, Pro::Plain, pl_o, p, pdl))) return rc;
+                ML2_NCCL(g_nccl.AllReduce(m->partial, m->partial, dim, ncclFloat, ncclSum, m->comm, ctx->stream));
+                if ((rc = launch_k(m, "residual_add", residual_add_f32_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, false, m->x,
+                                   (const float*)m->partial, dim)))
+                    return rc;
+            } else {
+                p.out[0] = m->x;
+                if ((rc = launch_matvec(ctx, Fmt::Int4, Epi::Residual, Pro::Plain, pl_o, p, pdl))) return rc;
+            }
+        }
+        {   // 4. rmsnorm + gate/up + swiglu (:179-181)
+            MatVecParams p{};
+            p.mat[0] = qwp(L.gate); p.mat[1] = qwp(L.up); p.out[0] = m->h;
+            p.in = m->x; p.gamma = L.rms_ffn; p.eps = m->eps;
+            p.rows = dim; p.cols = m->hidden_local; p.nmat = 2;
+            if ((rc = launch_matvec(ctx, Fmt::Int4, Epi::SwiGLU, Pro::RMSNorm, pl_gu, p, pdl && m->tp == 1))) return rc;
+        }
+        {   // 5. down + residual (:183)
+            MatVecParams p{};
+            p.mat[0] = qwp(L.down); p.in = m->h; p.rows = m->hidden_local; p.cols = dim; p.nmat = 1;
+            if (m->tp > 1) {
+                p.out_f32 = m->partial;
+                if ((rc = launch_matvec(ctx, Fmt::Int4, Epi::PartialF32, Pro::Plain, pl_down, p, pdl))) return rc;
+                ML2_NCCL(g_nccl.AllReduce(m->partial, m->partial, dim, ncclFloat, ncclSum, m->comm, ctx->stream));
+                if ((rc = launch_k(m, "residual_add", residual_add_f32_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, false, m->x,
+                                   (const float*)m->partial, dim)))
+                    return rc;
+            } else {
+                p.out[0] = m->x;
+                if ((rc = launch_matvec(ctx, Fmt::Int4, Epi::Residual, Pro::Plain, pl_down, p, pdl))) return rc;
+            }
+        }
+    }
+    {   // final rmsnorm + classifier (:187-189)
+        MatVecParams p{};
+        p.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
+        p.out[0] = m->tp > 1 ? m->logits_local : m->logits;
+        p.in = m->x; p.gamma = m->rms_final; p.eps = m->eps;
+        p.rows = dim; p.cols = m->vocab_local; p.nmat = 1;
+        if ((rc = launch_matvec(ctx, Fmt::F16, Epi::Store, Pro::RMSNorm, pl_cls, p, pdl && m->tp == 1))) return rc;
+        if (m->tp > 1)
+            ML2_NCCL(g_nccl.AllGather(m->logits_local, m->logits, m->vocab_local, ncclHalf, m->comm, ctx->stream));
+    }
+    if ((rc = launch_k(m, "argmax", argmax_step_kernel, dim3(1), dim3(1024), 0, m->tp == 1, (const __half*)m->logits, c.vocab_size,
+                       m->tokens, (const StepState*)m->step)))
+        return rc;
+    m->launches_per_token = ctx->launches - before;
+    return ML2_OK;
+}
+
+
+// Launches one kernel kind of one layer exactly as the token sequence does (no NCCL, no PDL); used by the
+// profiler below. kind: 0 qkv, 1 attention, 2 o-proj, 3 gate/up, 4 down, 5 classifier.
+static int enqueue_kind(Model* m, int kind, int l)
+{
+    Ctx* ctx = m->ctx;
+    const ml2_config& c = m->cfg;
+    const int dim = c.dim;
+    int rc;
+    MatVecPlan pl;
+    const size_t kv_layer = (size_t)c.seq_len * m->dim_local;
+    const LayerW& L = m->layers[l];
+    __half* kc = m->key_cache + (size_t)l * kv_layer;
+    __half* vc = m->value_cache + (size_t)l * kv_layer;
+    MatVecParams p{};
+    switch (kind) {
+    case 0:
+        if ((rc = plan_matvec(ctx, Fmt::Int4, Epi::QKVRope, dim, m->dim_local, 3, &pl))) return rc;
+        p.mat[0] = qwp(L.q); p.mat[1] = qwp(L.k); p.mat[2] = qwp(L.v);
+        p.out[0] = m->q; p.out[1] = kc; p.out[2] = vc;
+        p.in = m->x; p.gamma = L.rms_att; p.eps = m->eps;
+        p.rope_table = m->rope_table; p.pos_ptr = &m->step->pos; p.kv_row_stride = m->dim_local;
+        p.rows = dim; p.cols = m->dim_local; p.nmat = 3; p.head_size = m->head_size;
+        return launch_matvec(ctx, Fmt::Int4, Epi::QKVRope, Pro::RMSNorm, pl, p, false);
+    case 1: {
+        AttnParams a{};
+        const int chunk_cap = std::max(ceil_div(c.seq_len, kAttnCluster), kAttnSingleCtaMax);
+        a.out = m->xb; a.q = m->q; a.k = kc; a.v = vc; a.pos_ptr = &m->step->pos;
+        a.n_heads = m->heads_local; a.head_size = m->head_size; a.row_stride = m->dim_local;
+        a.scale = 1.0f / sqrtf((float)m->head_size); a.chunk_cap = chunk_cap;
+        const bool save = m->use_pdl;
+        m->use_pdl = false;
+        rc = launch_k(m, "attention", fused_attention_kernel, dim3(m->heads_local * kAttnCluster), dim3(kAttnThreads),
+                      (size_t)chunk_cap * sizeof(float), false, a);
+        m->use_pdl = save;
+        return rc;
+    }
+    case 2:
+    case 4: {
+        const int rows = kind == 2 ? m->dim_local : m->hidden_local;
+        const Epi e = m->tp > 1 ? Epi::PartialF32 : Epi::Residual;
+        if ((rc = plan_matvec(ctx, Fmt::Int4, e, rows, dim, 1, &pl))) return rc;
+        p.mat[0] = qwp(kind == 2 ? L.o : L.down); p.in = kind == 2 ? m->xb : m->h; p.rows = rows; p.cols = dim; p.nmat = 1;
+        p.out[0] = m->x; p.out_f32 = m->partial;
+        return launch_matvec(ctx, Fmt::Int4, e, Pro::Plain, pl, p, false);
+    }
+    case 3:
+        if ((rc = plan_matvec(ctx, Fmt::Int4, Epi::SwiGLU, dim, m->hidden_local, 2, &pl))) return rc;
+        p.mat[0] = qwp(L.gate); p.mat[1] = qwp(L.up); p.out[0] = m->h;
+        p.in = m->x; p.gamma = L.rms_ffn; p.eps = m->eps;
+        p.rows = dim; p.cols = m->hidden_local; p.nmat = 2;
+        return launch_matvec(ctx, Fmt::Int4, Epi::SwiGLU, Pro::RMSNorm, pl, p, false);
+    case 5:
+        if ((rc = plan_matvec(ctx, Fmt::F16, Epi::Store, dim, m->vocab_local, 1, &pl))) return rc;
+        p.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
+        p.out[0] = m->tp > 1 ? m->logits_local : m->logits;
+        p.in = m->x; p.gamma = m->rms_final; p.eps = m->eps;
+        p.rows = dim; p.cols = m->vocab_local; p.nmat = 1;
+        return launch_matvec(ctx, Fmt::F16, Epi::Store, Pro::RMSNorm, pl, p, false);
+    }
+    return fail(ML2_E_INVALID, "profile: kind %d", kind);
+}
+
+static double qweight_bytes(int rows, int cols)
+{
+    const int ss = ceil_div(rows, kGroup), ws = ceil_div(rows, 32) * 4, zs = ceil_div(ss, 8);
+    return (double)cols * (ws * 4.0 + zs * 4.0 + ss * 2.0);
+}
+
+static int check_bound(Model* m)
+{
+    if (!m->embed || !m->classifier || !m->rms_final) return fail(ML2_E_STATE, "model: globals are not bound");
+    for (size_t l = 0; l < m->layers.size(); ++l)
+        if (!m->layers[l].bound) return fail(ML2_E_STATE, "model: layer %zu is not bound", l);
+    if (!m->x) return fail(ML2_E_STATE, "model: run state is not allocated or bound");
+    return ML2_OK;
+}
+
+}  // namespace ml2
+
+using namespace ml2;
+
+extern "C" {
+
+int ml2_nccl_unique_id(void* out128)
+{
+    if (!out128) return fail(ML2_E_INVALID, "ml2_nccl_unique_id: null buffer");
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId size");
+    int rc = nccl_load();
+    if (rc) return rc;
+    ncclUniqueId id;
+    ML2_NCCL(g_nccl.GetUniqueId(&id));
+    memcpy(out128, &id, sizeof(id));
+    return ML2_OK;
+}
+
+int ml2_model_create(ml2_ctx* h, const ml2_config* cfg, int tp_size, int tp_rank, const void* nccl_id128, ml2_model** out)
+{
+    Ctx* ctx = reinterpret_cast<Ctx*>(h);
+    if (!ctx || !cfg || !out) return fail(ML2_E_INVALID, "ml2_model_create: null argument");
+    const ml2_config& c = *cfg;
+    if (c.dim <= 0 || c.hidden_dim <= 0 || c.n_layers <= 0 || c.n_heads <= 0 || c.vocab_size <= 0 || c.seq_len <= 0)
+        return fail(ML2_E_INVALID, "ml2_model_create: non-positive config field");
+    if (c.n_kv_heads != c.n_heads)
+        return fail(ML2_E_INVALID, "grouped-query attention (numKVHeads != numHeads) is not supported, as in the reference");
+    if (c.dim % c.n_heads) return fail(ML2_E_INVALID, "dim %d is not a multiple of n_heads %d", c.dim, c.n_heads);
+    const int hs = c.dim / c.n_heads;
+    if (hs != kHeadMax) return fail(ML2_E_INVALID, "head size %d: the fused path supports 128 only", hs);
+    if (c.dim % kGroup || c.hidden_dim % kGroup) return fail(ML2_E_INVALID, "dim and hidden_dim must be multiples of 128");
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return fail(ML2_E_INVALID, "tp_size=%d tp_rank=%d", tp_size, tp_rank);
+    if (c.n_heads % tp_size) return fail(ML2_E_INVALID, "n_heads %d is not divisible by tp %d", c.n_heads, tp_size);
+    if (c.vocab_size % tp_size) return fail(ML2_E_INVALID, "vocab_size %d is not divisible by tp %d", c.vocab_size, tp_size);
+    if (tp_size > 1 && !nccl_id128) return fail(ML2_E_INVALID, "tp > 1 needs the shared NCCL unique id");
+
+    ML2_CUDA(cudaSetDevice(ctx->device));
+    Model* m = new Model();
+    m->ctx = ctx;
+    m->cfg = c;
+    m->tp = tp_size;
+    m->rank = tp_rank;
+    m->head_size = hs;
+    m->heads_local = c.n_heads / tp_size;
+    m->dim_local = m->heads_local * hs;
+    int g0, ng;
+    ml2_tp_hidden_groups(c.hidden_dim, tp_size, tp_rank, &g0, &ng);
+    m->hidden_local = ng * kGroup;
+    m->vocab_local = c.vocab_size / tp_size;
+    m->vocab_row0 = m->vocab_local * tp_rank;
+    m->layers.resize(c.n_layers);
+    const char* eg = getenv("ML2_NO_GRAPH");
+    m->use_graph = !(eg && *eg == '1');
+    const char* ep = getenv("ML2_NO_PDL");
+    m->use_pdl = !(ep && *ep == '1');
+    ML2_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    ctx->stream = m->stream;
+    int rc;
+    if ((rc = dev_alloc(m, (void**)&m->step, sizeof(StepState)))) return rc;
+    if ((rc = dev_alloc(m, (void**)&m->rope_table, (size_t)c.seq_len * (hs / 2) * sizeof(float2)))) return rc;
+    rope_table_kernel<<<ceil_div(c.seq_len * (hs / 2), 256), 256, 0, m->stream>>>(m->rope_table, c.seq_len, hs, c.rope_theta);
+    ++ctx->launches;
+    if (tp_size > 1) {
+        if ((rc = dev_alloc(m, (void**)&m->partial, (size_t)c.dim * sizeof(float)))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->logits_local, (size_t)m->vocab_local * sizeof(__half)))) return rc;
+        if ((rc = nccl_load())) return rc;
+        ncclUniqueId id;
+        memcpy(&id, nccl_id128, sizeof(id));
+        ML2_NCCL(g_nccl.CommInitRank(&m->comm, tp_size, id, tp_rank));
+    }
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    *out = reinterpret_cast<ml2_model*>(m);
+    return ML2_OK;
+}
+
+void ml2_tp_hidden_groups(int hidden_dim, int tp_size, int tp_rank, int* g0, int* ngroups)
+{
+    // whole groups of 128, the first (groups % tp) ranks take one more
+    const int groups = hidden_dim / kGroup;
+    const int base = groups / tp_size, extra = groups % tp_size;
+    const int n = base + (tp_rank < extra ? 1 : 0);
+    const int start = tp_rank * base + (tp_rank < extra ? tp_rank : extra);
+    if (g0) *g0 = start;
+    if (ngroups) *ngroups = n;
+}
+
+int ml2_model_destroy(ml2_model* h)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return ML2_OK;
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->stream);
+    if (m->exec) cudaGraphExecDestroy(m->exec);
+    if (m->graph) cudaGraphDestroy(m->graph);
+    if (m->comm) g_nccl.CommDestroy(m->comm);
+    for (void* p : m->owned) cudaFree(p);
+    if (m->ctx->stream == m->stream) m->ctx->stream = nullptr;
+    cudaStreamDestroy(m->stream);
+    delete m;
+    return ML2_OK;
+}
+
+int ml2_model_local_shape(ml2_model* h, int* dim_local, int* hidden_local, int* vocab_local, int* hidden_group0, int* vocab_row0)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    int g0, ng;
+    ml2_tp_hidden_groups(m->cfg.hidden_dim, m->tp, m->rank, &g0, &ng);
+    if (dim_local) *dim_local = m->dim_local;
+    if (hidden_local) *hidden_local = m->hidden_local;
+    if (vocab_local) *vocab_local = m->vocab_local;
+    if (hidden_group0) *hidden_group0 = g0;
+    if (vocab_row0) *vocab_row0 = m->vocab_row0;
+    return ML2_OK;
+}
+
+int ml2_model_bind_globals(ml2_model* h, const void* embed, const void* classifier_local, const void* rms_final)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !embed || !classifier_local || !rms_final) return fail(ML2_E_INVALID, "bind_globals: null argument");
+    if ((reinterpret_cast<uintptr_t>(classifier_local) & 15u) || (reinterpret_cast<uintptr_t>(rms_final) & 15u))
+        return fail(ML2_E_INVALID, "bind_globals: classifier and norm weights must be 16-byte aligned");
+    m->embed = static_cast<const __half*>(embed);
+    m->classifier = static_cast<const __half*>(classifier_local);
+    m->rms_final = static_cast<const __half*>(rms_final);
+    return ML2_OK;
+}
+
+int ml2_model_bind_layer(ml2_model* h, int layer, const ml2_layer_weights* w)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !w) return fail(ML2_E_INVALID, "bind_layer: null argument");
+    if (layer < 0 || layer >= m->cfg.n_layers) return fail(ML2_E_INVALID, "bind_layer: layer %d out of range", layer);
+    const ml2_qweight* all[7] = {&w->query, &w->key, &w->value, &w->output, &w->gate, &w->up, &w->down};
+    for (const ml2_qweight* q : all) {
+        if (!q->weight || !q->zeros || !q->scales) return fail(ML2_E_INVALID, "bind_layer: null QWeight array");
+        if ((reinterpret_cast<uintptr_t>(q->weight) & 15u) || (reinterpret_cast<uintptr_t>(q->zeros) & 15u) ||
+            (reinterpret_cast<uintptr_t>(q->scales) & 15u))
+            return fail(ML2_E_INVALID, "bind_layer: QWeight arrays must be 16-byte aligned");
+    }
+    if (!w->rms_attention || !w->rms_feed_forward || (reinterpret_cast<uintptr_t>(w->rms_attention) & 15u) ||
+        (reinterpret_cast<uintptr_t>(w->rms_feed_forward) & 15u))
+        return fail(ML2_E_INVALID, "bind_layer: norm weights must be non-null and 16-byte aligned");
+    LayerW& L = m->layers[layer];
+    L.q = w->query; L.k = w->key; L.v = w->value; L.o = w->output; L.gate = w->gate; L.up = w->up; L.down = w->down;
+    L.rms_att = static_cast<const __half*>(w->rms_attention);
+    L.rms_ffn = static_cast<const __half*>(w->rms_feed_forward);
+    L.bound = true;
+    if (m->exec) { cudaGraphExecDestroy(m->exec); m->exec = nullptr; }
+    return ML2_OK;
+}
+
+int ml2_model_alloc_runstate(ml2_model* h)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    if (m->x) return fail(ML2_E_STATE, "run state already present");
+    const ml2_config& c = m->cfg;
+    int rc;
+    const size_t kv = (size_t)c.n_layers * c.seq_len * m->dim_local * sizeof(__half);
+    if ((rc = dev_alloc(m, (void**)&m->x, (size_t)c.dim * 2)) || (rc = dev_alloc(m, (void**)&m->xb, (size_t)c.dim * 2)) ||
+        (rc = dev_alloc(m, (void**)&m->h, (size_t)c.hidden_dim * 2)) || (rc = dev_alloc(m, (void**)&m->q, (size_t)c.dim * 2)) ||
+        (rc = dev_alloc(m, (void**)&m->logits, (size_t)c.vocab_size * 2)) || (rc = dev_alloc(m, (void**)&m->key_cache, kv)) ||
+        (rc = dev_alloc(m, (void**)&m->value_cache, kv)) || (rc = dev_alloc(m, (void**)&m->tokens, (size_t)(c.seq_len + 1) * sizeof(int))))
+        return rc;
+    m->own_state = true;
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_bind_runstate(ml2_model* h, const ml2_runstate* rs)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !rs) return fail(ML2_E_INVALID, "bind_runstate: null argument");
+    if (m->own_state) return fail(ML2_E_STATE, "run state already allocated by the library");
+    void* all[] = {rs->x, rs->xb, rs->h, rs->q, rs->logits, rs->key_cache, rs->value_cache, rs->tokens};
+    for (void* p : all)
+        if (!p || (reinterpret_cast<uintptr_t>(p) & 15u)) return fail(ML2_E_INVALID, "bind_runstate: buffers must be non-null and 16-byte aligned");
+    m->x = (__half*)rs->x; m->xb = (__half*)rs->xb; m->h = (__half*)rs->h; m->q = (__half*)rs->q; m->logits = (__half*)rs->logits;
+    m->key_cache = (__half*)rs->key_cache; m->value_cache = (__half*)rs->value_cache; m->tokens = (int*)rs->tokens;
+    if (m->exec) { cudaGraphExecDestroy(m->exec); m->exec = nullptr; }
+    return ML2_OK;
+}
+
+int ml2_model_runstate(ml2_model* h, ml2_runstate* rs)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !rs) return fail(ML2_E_INVALID, "runstate: null argument");
+    rs->x = m->x; rs->xb = m->xb; rs->h = m->h; rs->q = m->q; rs->logits = m->logits;
+    rs->key_cache = m->key_cache; rs->value_cache = m->value_cache; rs->tokens = m->tokens;
+    return ML2_OK;
+}
+
+int ml2_model_forward(ml2_model* h, int pos, int next_pos, int write_token)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    int rc = check_bound(m);
+    if (rc) return rc;
+    if (pos < 0 || pos >= m->cfg.seq_len || next_pos < 0 || next_pos > m->cfg.seq_len)
+        return fail(ML2_E_INVALID, "forward: pos=%d next_pos=%d outside [0,%d)", pos, next_pos, m->cfg.seq_len);
+    Ctx* ctx = m->ctx;
+    ctx->stream = m->stream;
+    if (!m->use_graph) return enqueue_token(m, pos, next_pos, write_token);
+
+    if (!m->exec) {
+        if (m->graph) { cudaGraphDestroy(m->graph); m->graph = nullptr; }
+        const long long before = ctx->launches;
+        ML2_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        rc = enqueue_token(m, pos, next_pos, write_token);
+        cudaGraph_t g = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+        ctx->launches = before;  // captured, not launched
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) return fail(ML2_E_CUDA, "graph capture: %s", cudaGetErrorString(e));
+        m->graph = g;
+        ML2_CUDA(cudaGraphInstantiate(&m->exec, m->graph, 0));
+        // the first kernel node carries the step; find it (root node of the captured chain)
+        size_t n_roots = 0;
+        ML2_CUDA(cudaGraphGetRootNodes(m->graph, nullptr, &n_roots));
+        std::vector<cudaGraphNode_t> roots(n_roots);
+        ML2_CUDA(cudaGraphGetRootNodes(m->graph, roots.data(), &n_roots));
+        m->first_node = nullptr;
+        for (cudaGraphNode_t nd : roots) {
+            cudaGraphNodeType t;
+            ML2_CUDA(cudaGraphNodeGetType(nd, &t));
+            if (t == cudaGraphNodeTypeKernel) { m->first_node = nd; break; }
+        }
+        if (!m->first_node) return fail(ML2_E_CUDA, "graph capture: first kernel node not found");
+    }
+    // refresh the step carried by the first node, then replay
+    cudaKernelNodeParams kp{};
+    ML2_CUDA(cudaGraphKernelNodeGetParams(m->first_node, &kp));
+    StepState* st = m->step;
+    __half* x = m->x;
+    const __half* table = m->embed;
+    int dim = m->cfg.dim;
+    const int* tokens = m->tokens;
+    void* args[] = {&st, &pos, &next_pos, &write_token, &x, &table, &dim, &tokens};
+    kp.kernelParams = args;
+    ML2_CUDA(cudaGraphExecKernelNodeSetParams(m->exec, m->first_node, &kp));
+    ML2_CUDA(cudaGraphLaunch(m->exec, m->stream));
+    ctx->launches += m->launches_per_token;
+    return ML2_OK;
+}
+
+long long ml2_model_launches_per_token(ml2_model* h) { return h ? reinterpret_cast<Model*>(h)->launches_per_token : 0; }
+
+int ml2_model_synchronize(ml2_model* h)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_set_tokens(ml2_model* h, const int* tokens_host, int first, int count)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !tokens_host) return fail(ML2_E_INVALID, "set_tokens: null argument");
+    if (!m->tokens) return fail(ML2_E_STATE, "set_tokens: run state missing");
+    if (first < 0 || count < 0 || first + count > m->cfg.seq_len + 1) return fail(ML2_E_INVALID, "set_tokens: range");
+    ML2_CUDA(cudaMemcpyAsync(m->tokens + first, tokens_host, (size_t)count * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_put_token_async(ml2_model* h, int pos, const int* token_pinned_host)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !token_pinned_host) return fail(ML2_E_INVALID, "put_token_async: null argument");
+    if (!m->tokens) return fail(ML2_E_STATE, "put_token_async: run state missing");
+    if (pos < 0 || pos > m->cfg.seq_len) return fail(ML2_E_INVALID, "put_token_async: pos");
+    ML2_CUDA(cudaMemcpyAsync(m->tokens + pos, token_pinned_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_read_token(ml2_model* h, int pos, int* token_host)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !token_host) return fail(ML2_E_INVALID, "read_token: null argument");
+    if (pos < 0 || pos > m->cfg.seq_len) return fail(ML2_E_INVALID, "read_token: pos");
+    // the reference's only per-token synchronisation: a 4-byte blocking read (src/Sampler.cs:69)
+    ML2_CUDA(cudaMemcpyAsync(token_host, m->tokens + pos, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_read_logits(ml2_model* h, void* logits_host_f16)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !logits_host_f16) return fail(ML2_E_INVALID, "read_logits: null argument");
+    ML2_CUDA(cudaMemcpyAsync(logits_host_f16, m->logits, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_stream(ml2_model* h, void** stream)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !stream) return fail(ML2_E_INVALID, "model_stream: null argument");
+    *stream = m->stream;
+    return ML2_OK;
+}
+
+int ml2_model_profile(ml2_model* h, int iters, double* avg_us, double* algo_bytes)
+{
+    // Times every kernel kind on its own: `iters` sweeps over all layers (distinct weights every launch, the
+    // sweep is far larger than L2), CUDA events on the model's stream. Activations are whatever the last
+    // forward left; the residual stream is restored afterwards.
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !avg_us || !algo_bytes) return fail(ML2_E_INVALID, "profile: null argument");
+    int rc = check_bound(m);
+    if (rc) return rc;
+    if (iters < 1) return fail(ML2_E_INVALID, "profile: iters=%d", iters);
+    Ctx* ctx = m->ctx;
+    ctx->stream = m->stream;
+    const ml2_config& c = m->cfg;
+    __half* x_save = nullptr;
+    ML2_CUDA(cudaMalloc(&x_save, (size_t)c.dim * 2));
+    ML2_CUDA(cudaMemcpyAsync(x_save, m->x, (size_t)c.dim * 2, cudaMemcpyDeviceToDevice, m->stream));
+    int pos = 0;
+    ML2_CUDA(cudaMemcpyAsync(&pos, &m->step->pos, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    cudaEvent_t e0, e1;
+    ML2_CUDA(cudaEventCreate(&e0));
+    ML2_CUDA(cudaEventCreate(&e1));
+    const double n = pos + 1;
+    const double kv_bytes = 2.0 * n * m->dim_local * 2.0 + 2.0 * m->dim_local * 2.0;
+    const double bytes[6] = {
+        3.0 * qweight_bytes(c.dim, m->dim_local) + 2.0 * c.dim * 2 + 3.0 * m->dim_local * 2,
+        kv_bytes,
+        qweight_bytes(m->dim_local, c.dim) + m->dim_local * 2.0 + 2.0 * c.dim * 2,
+        2.0 * qweight_bytes(c.dim, m->hidden_local) + 2.0 * c.dim * 2 + m->hidden_local * 2.0,
+        qweight_bytes(m->hidden_local, c.dim) + m->hidden_local * 2.0 + 2.0 * c.dim * 2,
+        (double)m->vocab_local * c.dim * 2 + 2.0 * c.dim * 2 + m->vocab_local * 2.0};
+    for (int kind = 0; kind < 6; ++kind) {
+        const int per_iter = kind == 5 ? 1 : c.n_layers;
+        const int reps = kind == 5 ? iters * 4 : iters;
+        for (int l = 0; l < per_iter; ++l)
+            if ((rc = enqueue_kind(m, kind, l))) return rc;  // warm-up sweep
+        ML2_CUDA(cudaEventRecord(e0, m->stream));
+        for (int it = 0; it < reps; ++it)
+            for (int l = 0; l < per_iter; ++l)
+                if ((rc = enqueue_kind(m, kind, l))) return rc;
+        ML2_CUDA(cudaEventRecord(e1, m->stream));
+        ML2_CUDA(cudaEventSynchronize(e1));
+        float ms = 0.f;
+        ML2_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        avg_us[kind] = (double)ms * 1e3 / ((double)reps * per_iter);
+        algo_bytes[kind] = bytes[kind];
+    }
+    ML2_CUDA(cudaMemcpyAsync(m->x, x_save, (size_t)c.dim * 2, cudaMemcpyDeviceToDevice, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    cudaFree(x_save);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return ML2_OK;
+}
+
+int ml2_model_generate(ml2_model* h, const int* prompt_host, int n_prompt, int steps, int* out_tokens_host, int* n_out)
+{
+    // Transformer.Generate (src/Transformer.cs:89-112) on token ids: prompt to the device once, then per
+    // position one Forward and, past the prompt, the greedy sample read back as 4 bytes; stops on id < 3.
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !prompt_host || !out_tokens_host || !n_out) return fail(ML2_E_INVALID, "generate: null argument");
+    if (n_prompt < 1 || steps < 0 || steps > m->cfg.seq_len - 1) return fail(ML2_E_INVALID, "generate: n_prompt=%d steps=%d", n_prompt, steps);
+    if (n_prompt > m->cfg.seq_len) return fail(ML2_E_INVALID, "generate: prompt longer than the sequence length");
+    int rc = ml2_model_set_tokens(h, prompt_host, 0, n_prompt);
+    if (rc) return rc;
+    int produced = 0;
+    for (int pos = 0; pos < steps; ++pos) {
+        const int next_pos = pos + 1;
+        const int generate = next_pos >= n_prompt;
+        if ((rc = ml2_model_forward(h, pos, next_pos, generate))) return rc;
+        int token;
+        if (generate) {
+            if ((rc = ml2_model_read_token(h, next_pos, &token))) return rc;
+        } else {
+            token = prompt_host[next_pos];
+        }
+        if (token < 3) break;
+        out_tokens_host[produced++] = token;
+    }
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    *n_out = produced;
+    return ML2_OK;
+}
+
+}  // extern "C"

@@ -41,7 +41,7 @@ __device__ __forceinline__ float block_max(float v, float* s_buf)
 
 // ---- RMSNorm (native/rmsnorm_kernel.cu:8-42): fp32 squares, rms = 1/sqrtf(ss/n + eps),
 // out = half(rms * gamma * x), one block. out may alias in.
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(__half* out, const __half* in, const __half* gamma, int size, float eps)
+static __global__ void __launch_bounds__(1024) rmsnorm_kernel(__half* out, const __half* in, const __half* gamma, int size, float eps)
 {
     __shared__ float s_buf[33];
     pdl_wait();
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(__half* out, const __half
 
 // ---- RoPE (native/rope_kernel.cu:3-31): rotate-half pairs (t, t + hs/2) in every head; q always,
 // k for heads below n_kv_heads; angle = pos / theta^(2t/hs) with powf/cosf/sinf.
-__global__ void rope_kernel(__half* q, __half* k, int n_heads, int n_kv_heads, int head_size, int pos, float theta)
+static __global__ void rope_kernel(__half* q, __half* k, int n_heads, int n_kv_heads, int head_size, int pos, float theta)
 {
     pdl_wait();
     const int half_hs = head_size >> 1;
@@ -83,7 +83,7 @@ __global__ void rope_kernel(__half* q, __half* k, int n_heads, int n_kv_heads, i
 
 // (cos, sin) table for the fused QKV epilogue: same expressions as rope_kernel, one entry per
 // (position, pair index).
-__global__ void rope_table_kernel(float2* table, int seq_len, int head_size, float theta)
+static __global__ void rope_table_kernel(float2* table, int seq_len, int head_size, float theta)
 {
     const int half_hs = head_size >> 1;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -96,7 +96,7 @@ __global__ void rope_table_kernel(float2* table, int seq_len, int head_size, flo
 }
 
 // ---- embedding gather (native/embedding_kernel.cu:3-17)
-__global__ void embedding_kernel(__half* out, const __half* table, int size, const int* tokens, int pos)
+static __global__ void embedding_kernel(__half* out, const __half* table, int size, const int* tokens, int pos)
 {
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -106,7 +106,7 @@ __global__ void embedding_kernel(__half* out, const __half* table, int size, con
 }
 
 // ---- argmax (native/argmax_kernel.cu:8-46), lowest index wins ties
-__global__ void __launch_bounds__(1024) argmax_kernel(const __half* in, int size, int* result, int pos, int write_token)
+static __global__ void __launch_bounds__(1024) argmax_kernel(const __half* in, int size, int* result, int pos, int write_token)
 {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __half* in, int size
 // ---- attention scores (mat_vec_strided_kernel, native/mat_vec_kernel.cu:51-81):
 // att[h*seq + t] = half(scale * sum_d q[h*hs+d] * K[t*dim + h*hs + d]); one warp per (t, h),
 // 8-byte loads, grid sized by the live sequence length.
-__global__ void __launch_bounds__(256) attn_scores_kernel(__half* att, const __half* q, const __half* k, int head_size, int dim,
+static __global__ void __launch_bounds__(256) attn_scores_kernel(__half* att, const __half* q, const __half* k, int head_size, int dim,
                                                           int seq, float scale)
 {
     pdl_wait();
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(__half* att, const __h
 
 // ---- softmax (native/softmax_kernel.cu:10-52): per head over `size` fp16 scores, fp32 math,
 // in place. Three passes over L2-resident scores instead of a fixed shared-memory array.
-__global__ void __launch_bounds__(1024) softmax_kernel(__half* att, int size)
+static __global__ void __launch_bounds__(1024) softmax_kernel(__half* att, int size)
 {
     __shared__ float s_buf[33];
     pdl_wait();
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(1024) softmax_kernel(__half* att, int size)
 // ---- attention values (vec_mat_kernel, native/vec_mat_kernel.cu:8-48):
 // out[h*hs + d] = half(sum_t att[h*seq+t] * V[t*dim + h*hs + d]). Block per (head, 128-wide d slab):
 // warp w sweeps t = w, w+nw, ...; lane owns 4 consecutive d (8-byte loads); warps are summed in order.
-__global__ void __launch_bounds__(1024) attn_values_kernel(__half* out, const __half* att, const __half* v, int head_size, int dim,
+static __global__ void __launch_bounds__(1024) attn_values_kernel(__half* out, const __half* att, const __half* v, int head_size, int dim,
                                                            int seq)
 {
     __shared__ float s_acc[32][128 + 4];
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(1024) attn_values_kernel(__half* out, const __
 }
 
 // ---- dequantise to fp16, HostQWeight.Unpack (src/QWeight.cs:29-54) per output row
-__global__ void dequant_int4_kernel(__half* out, const uint32_t* w, const uint32_t* z, const __half* s, int rows, int cols,
+static __global__ void dequant_int4_kernel(__half* out, const uint32_t* w, const uint32_t* z, const __half* s, int rows, int cols,
                                     int wsize, int zsize, int ssize)
 {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one packed word each
@@ -294,7 +294,7 @@ __host__ __device__ __forceinline__ float synth_normal_f32(uint64_t key, uint64_
     return (float)(s - 262140) * (sigma * (1.0f / 53509.94f));
 }
 
-__global__ void synth_qweight_kernel(uint32_t* weight, uint32_t* zeros, __half* scales, int rows_full, int col0, int ncols, int g0,
+static __global__ void synth_qweight_kernel(uint32_t* weight, uint32_t* zeros, __half* scales, int rows_full, int col0, int ncols, int g0,
                                      int ngroups, uint64_t kw, uint64_t kz, uint64_t ks)
 {
     const int rows = min(ngroups * kGroup, rows_full - g0 * kGroup);
@@ -323,7 +323,7 @@ __global__ void synth_qweight_kernel(uint32_t* weight, uint32_t* zeros, __half* 
     }
 }
 
-__global__ void synth_normal_kernel(__half* out, long long row0, long long nrows, int width, float sigma, uint64_t key)
+static __global__ void synth_normal_kernel(__half* out, long long row0, long long nrows, int width, float sigma, uint64_t key)
 {
     const long long n = nrows * width;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
