@@ -126,6 +126,17 @@ int ml2_argmax(ml2_ctx* ctx, const void* logits, int vocab_size, int* tokens, in
  * device-resident weights, copies the result back and synchronises. */
 int ml2_matvec_residual_int4_host(ml2_ctx* ctx, void* inout_host, const void* in_host, const ml2_qweight* w_dev,
                                   int rows, int cols);
+/* No counterpart in the reference. Same operation and result as ml2_matvec_residual_int4_host, for hosts
+ * that must not see the library allocate: hosts that account for every device byte themselves (the
+ * reference's C# side owns all device buffers and sizes its KV cache from the free memory it sees), or that
+ * gave the whole device to one pool. The two vectors are staged in a fixed 64 KiB array inside the library
+ * image (held by every GPU that loads the library), so the call makes no cudaMalloc / cudaFree and uses no
+ * allocating routine. Limits: rows <= 16384 and cols <= 16384, larger sizes return ML2_E_INVALID. The first
+ * call on a device looks up the array's address (one-time set-up); make that first call outside any stream
+ * capture. All calls share the one array: calls whose GPU work overlaps (other streams, other threads or
+ * contexts of the same process) race on it - serialise them. */
+int ml2_matvec_residual_int4_host_static(ml2_ctx* ctx, void* inout_host, const void* in_host, const ml2_qweight* w_dev,
+                                         int rows, int cols);
 
 /* ---- synthetic tensors (counter-based, identical on host and device) ----------------------- */
 /* Fills the window [col0, col0+ncols) x groups [g0, g0+ngroups) of a logical rows_full-wide QWeight
