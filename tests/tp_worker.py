@@ -1,0 +1,67 @@
+"""Tensor-parallel worker (started by torch.distributed.run, one process per GPU): runs the sharded model for a few
+tokens and, on rank 0, compares the logits with the CPU oracle of the unsharded model."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    import managedllama2_b200 as ml2
+    import oracle
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        idt = torch.frombuffer(bytearray(ml2.Transformer.nccl_unique_id()), dtype=torch.uint8).cuda()
+    dist.broadcast(idt, 0)
+    # 8 heads, 13 hidden groups: uneven hidden split for 2, 4 and 8 ranks
+    cfg = ml2.Config(dim=1024, hiddenDim=13 * 128, numLayers=2, numHeads=8, numKVHeads=8, vocabSize=512, seqLength=40)
+    ctx = ml2.CudaContext(local)
+    w = ml2.synthetic_weights(ctx, cfg, seed=21, tp_size=world, tp_rank=rank)
+    tr = ml2.Transformer(cfg, w, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
+    toks = [5, 99, 256, 31]
+    tr.set_tokens(np.array(toks, dtype=np.int32))
+    cpu = None
+    if rank == 0:
+        hw = ml2.synthetic_weights_host(cfg, seed=21)
+        cpu = oracle.CpuModel(dict(dim=cfg.dim, hidden_dim=cfg.hiddenDim, n_layers=cfg.numLayers, n_heads=cfg.numHeads,
+                                   n_kv_heads=cfg.numKVHeads, vocab_size=cfg.vocabSize, seq_len=cfg.seqLength,
+                                   rope_theta=cfg.ropeTheta), hw, mode=1)
+    ok = True
+    for pos in range(12):
+        gen = pos + 1 >= len(toks)
+        tr.Forward(pos, pos + 1, gen)
+        logits = tr.logits()
+        # every rank must hold the same logits bit for bit
+        t = torch.from_numpy(logits.view(np.int16).astype(np.int32)).cuda()
+        lo, hi = t.clone(), t.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ok = ok and bool((lo == hi).all().item())
+        if gen:
+            toks.append(tr.read_token(pos + 1))
+        if rank == 0:
+            want = cpu.forward(toks[pos], pos).astype(np.float32)
+            err = float(np.abs(logits.astype(np.float32) - want).max())
+            ok = ok and err <= 1e-2 and err <= 2e-2 * want.std()
+    ok = ok and ctx.status() == (0, 0)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    tr.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("TP_OK" if flag.item() == 1 else "TP_FAIL", "world", world, flush=True)
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
