@@ -1,0 +1,162 @@
+"""Parity against the reference's OWN CUDA kernels (compiled unmodified into oracle/_ref/ by `make -C oracle ref`).
+
+North-star part 3: greedy decode on a seeded random-weight model reproduces the reference CUDA build's logits within
+1e-2 and its argmax tokens for 64 steps. Run here on the Llama-2-7B shape (BASELINE configs[2]) with the reference
+kernels launched in Transformer.Forward order with the Module launch shapes (oracle/ref_cuda.py). If a greedy token
+differs, the step must be a near-tie in the reference's own logits; decoding then continues on the reference's tokens
+so that all 64 steps are compared.
+"""
+import numpy as np
+import pytest
+
+from oracle import ref_cuda
+from helpers import dev_qweight, rand_qweight, rand_vec, rel_err, to_dev, to_host
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref/*.cubin not built")]
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    return ref_cuda.RefKernels()
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (11008, 4096), (5120, 5120), (13824, 5120)])
+def test_residual_matvec_vs_reference_kernel(kernels, rows, cols):
+    import torch
+    import managedllama2_b200 as ml2
+    rng = np.random.default_rng(rows + cols)
+    w, z, s = rand_qweight(rng, rows, cols)
+    x, res = rand_vec(rng, rows), rand_vec(rng, cols)
+    q = dev_qweight(w, z, s)
+    cfg = ml2.Config(cols, rows, 1, cols // 128, cols // 128, 32, 8)
+    ref = ref_cuda.RefModules(cfg, kernels)
+    d_ref, d_x = to_dev(res), to_dev(x)
+    ref.residual(d_ref.data_ptr(), d_x.data_ptr(), (q.Weight.data_ptr(), q.Zeros.data_ptr(), q.Scales.data_ptr()), rows, cols)
+    torch.cuda.synchronize()
+    ctx = ml2.CudaContext(0)
+    d_our = to_dev(res)
+    ml2.MatVecResidual(ctx).Forward(d_our, d_x, q, rows, cols)
+    ctx.synchronize()
+    assert rel_err(to_host(d_our), to_host(d_ref)) <= 1e-3
+    ctx.close()
+
+
+def test_swiglu_and_qkv_vs_reference_kernels(kernels):
+    import torch
+    import managedllama2_b200 as ml2
+    rng = np.random.default_rng(99)
+    rows, hid = 4096, 11008
+    cfg = ml2.Config(rows, hid, 1, 32, 32, 32, 8)
+    ref = ref_cuda.RefModules(cfg, kernels)
+    ctx = ml2.CudaContext(0)
+    x = to_dev(rand_vec(rng, rows, 0.3))
+    g, u = dev_qweight(*rand_qweight(rng, rows, hid)), dev_qweight(*rand_qweight(rng, rows, hid))
+    tp = lambda q: (q.Weight.data_ptr(), q.Zeros.data_ptr(), q.Scales.data_ptr())
+    o_ref = torch.zeros(hid, dtype=torch.float16, device="cuda")
+    o_our = torch.zeros_like(o_ref)
+    ref.swiglu(o_ref.data_ptr(), x.data_ptr(), tp(g), tp(u), rows, hid)
+    ml2.MatVecSwiGLU(ctx).Forward(o_our, x, g, u, rows, hid)
+    torch.cuda.synchronize(); ctx.synchronize()
+    assert rel_err(to_host(o_our), to_host(o_ref)) <= 2e-3
+    qs = [dev_qweight(*rand_qweight(rng, rows, rows)) for _ in range(3)]
+    outs_ref = [torch.zeros(rows, dtype=torch.float16, device="cuda") for _ in range(3)]
+    outs_our = [torch.zeros(rows, dtype=torch.float16, device="cuda") for _ in range(3)]
+    ref.qkv(*[t.data_ptr() for t in outs_ref], x.data_ptr(), *[tp(q) for q in qs], rows, rows)
+    ml2.QKVMatVec(ctx, cfg).Forward(outs_our[0], outs_our[1], outs_our[2], x, *qs, rows, rows, 0, 0)
+    torch.cuda.synchronize(); ctx.synchronize()
+    for a, b in zip(outs_our, outs_ref):
+        assert rel_err(to_host(a), to_host(b)) <= 1e-3
+    ctx.close()
+
+
+def test_small_ops_vs_reference_kernels(kernels):
+    """RMSNorm, RoPE (bit-exact: same device math functions), scores, softmax, values, argmax."""
+    import torch
+    import managedllama2_b200 as ml2
+    rng = np.random.default_rng(5)
+    dim, heads, seq = 4096, 32, 300
+    cfg = ml2.Config(dim, 11008, 1, heads, heads, 32000, 512)
+    ref = ref_cuda.RefModules(cfg, kernels)
+    ctx = ml2.CudaContext(0)
+    x, gamma = to_dev(rand_vec(rng, dim)), to_dev(rand_vec(rng, dim, 0.02))
+    a, b = torch.zeros(dim, dtype=torch.float16, device="cuda"), torch.zeros(dim, dtype=torch.float16, device="cuda")
+    ref.rmsnorm(a.data_ptr(), x.data_ptr(), gamma.data_ptr(), dim)
+    ml2.RMSNorm(ctx).Forward(b, x, gamma, dim)
+    torch.cuda.synchronize(); ctx.synchronize()
+    assert rel_err(to_host(b), to_host(a)) <= 1e-3
+    for pos in (0, 1, 18, 4095):
+        q0, k0 = rand_vec(rng, dim), rand_vec(rng, dim)
+        qa, ka, qb, kb = to_dev(q0), to_dev(k0), to_dev(q0), to_dev(k0)
+        ref.rope(qa.data_ptr(), ka.data_ptr(), pos, 10000.0)
+        ml2.RoPERotation(ctx, cfg).Forward(qb, kb, heads, 128, pos, 0, 10000.0)  # layerOffset 0, row offset pos*kvDim..
+        torch.cuda.synchronize(); ctx.synchronize()
+        # RoPERotation.Forward offsets the key pointer by pos*kvDim (src/RoPERotation.cs:22): give it a cache
+        kc = torch.zeros((pos + 1) * dim, dtype=torch.float16, device="cuda")
+        kc[pos * dim:] = to_dev(k0)
+        qc = to_dev(q0)
+        ml2.RoPERotation(ctx, cfg).Forward(qc, kc, heads, 128, pos, 0, 10000.0)
+        ctx.synchronize()
+        assert np.array_equal(to_host(qc).view(np.uint16), to_host(qa).view(np.uint16))
+        assert np.array_equal(to_host(kc[pos * dim:]).view(np.uint16), to_host(ka).view(np.uint16))
+    q = to_dev(rand_vec(rng, dim))
+    kcache, vcache = to_dev(rand_vec(rng, seq * dim)), to_dev(rand_vec(rng, seq * dim))
+    att_a = torch.zeros(heads * dim, dtype=torch.float16, device="cuda")
+    att_b = torch.zeros_like(att_a)
+    scale = 1.0 / np.sqrt(128.0)
+    ref.scores(att_a.data_ptr(), q.data_ptr(), kcache.data_ptr(), seq, scale)
+    ml2.MatVecStrided(ctx, cfg).Forward(att_b, q, kcache, 128, dim, seq, 0, scale)
+    torch.cuda.synchronize(); ctx.synchronize()
+    assert rel_err(to_host(att_b)[:heads * seq], to_host(att_a)[:heads * seq]) <= 1e-3
+    att_b.copy_(att_a)
+    ref.softmax(att_a.data_ptr(), seq)
+    ml2.Softmax(ctx, cfg).Forward(att_b, seq)
+    torch.cuda.synchronize(); ctx.synchronize()
+    assert rel_err(to_host(att_b)[:heads * seq], to_host(att_a)[:heads * seq]) <= 1e-3
+    oa, ob = torch.zeros(dim, dtype=torch.float16, device="cuda"), torch.zeros(dim, dtype=torch.float16, device="cuda")
+    ref.vecmat(oa.data_ptr(), vcache.data_ptr(), att_a.data_ptr(), seq)
+    ml2.VecMat(ctx, cfg).Forward(ob, vcache, att_a, 128, dim, seq, 0)
+    torch.cuda.synchronize(); ctx.synchronize()
+    assert rel_err(to_host(ob), to_host(oa)) <= 1e-3
+    ctx.close()
+
+
+def test_greedy_decode_7b_shape_vs_reference_cuda_build(kernels):
+    import torch
+    import managedllama2_b200 as ml2
+    prompt_len, gen = 16, 64
+    cfg = ml2.Config(dim=4096, hiddenDim=11008, numLayers=32, numHeads=32, numKVHeads=32, vocabSize=32000,
+                     seqLength=prompt_len + gen + 4)
+    ctx = ml2.CudaContext(0)
+    w = ml2.synthetic_weights(ctx, cfg, seed=31415)
+    ours = ml2.Transformer(cfg, w, ctx)
+    ref = ref_cuda.RefTransformer(cfg, w, kernels)
+    rng = np.random.default_rng(31415)
+    prompt = rng.integers(3, cfg.vocabSize, size=prompt_len).astype(np.int32)
+    ours.set_tokens(prompt)
+    ref.set_tokens(prompt)
+    worst, flips, checked = 0.0, 0, 0
+    for pos in range(prompt_len + gen - 1):
+        generate = pos + 1 >= prompt_len
+        ref.forward(pos, pos + 1, generate)
+        ours.Forward(pos, pos + 1, generate)
+        torch.cuda.synchronize()
+        a, b = ours.logits().astype(np.float32), ref.logits_host().astype(np.float32)
+        err = float(np.abs(a - b).max())
+        worst = max(worst, err)
+        assert err <= 1e-2, (pos, err)
+        assert err <= 5e-2 * b.std(), (pos, err, b.std())
+        if generate:
+            checked += 1
+            t_ref, t_our = ref.read_token(pos + 1), ours.read_token(pos + 1)
+            if t_ref != t_our:
+                # allowed only when the reference's own top two logits are closer than the observed logits error
+                top2 = np.sort(b)[-2:]
+                assert top2[1] - top2[0] <= 2 * err + 1e-7, (pos, t_ref, t_our, top2, err)
+                flips += 1
+                ours.set_tokens(np.array([t_ref], dtype=np.int32), first=pos + 1)  # continue on the reference's tokens
+    assert checked == gen
+    assert flips <= 2
+    print("7B-shape greedy decode vs reference CUDA kernels: max |dlogit| = %.3e over %d steps, %d near-tie flips" %
+          (worst, prompt_len + gen - 1, flips))
+    ours.close()
+    ctx.close()
