@@ -1,0 +1,633 @@
+// One persistent kernel per token: the whole operator sequence of Transformer.Forward
+// (src/Transformer.cs:158-190 of GilesBathgate/ManagedLlama2) runs inside a single cooperative launch with
+// one CTA per SM, so HBM streaming never stops at an operator boundary.
+//
+//   * producer warp   walks the token's operator list and streams every weight tile this CTA owns, operator
+//                     after operator, into one shared-memory ring (1-D bulk async copies, mbarrier completion).
+//                     Weights do not depend on activations, so it runs ahead of the arithmetic by the depth of
+//                     the ring, across operator boundaries.
+//   * consumer warps  organised in groups of `kw` warps (one group spans a whole weight row: lane owns 32 inputs
+//                     = one 16-byte weight vector of every row). A group waits until the operator's input vector
+//                     is complete (a device-wide counter, acquire), keeps its slice in registers (RMSNorm applied
+//                     on the fly where the reference runs rmsnorm first), then takes tiles from the ring.
+//   * finalizer warps sum the k-warp partials in a fixed order and run the operator's tail (residual add, RoPE,
+//                     SwiGLU, stores) with the reference's fp16 rounding points; after its last tile of an
+//                     operator a CTA publishes "my share is done" (release) on that operator's counter.
+//   * attention       is an operator without weights: CTA h handles head h with the same three steps and rounding
+//                     points as the reference's scores / softmax / values kernels.
+//
+// Every wait is bounded; when a limit runs out the CTA records an error word, stops waiting and runs to its end.
+#pragma once
+
+#include "stream_matvec.cuh"
+
+namespace ml2 {
+
+enum MegaOpKind : int { MOP_QKV = 0, MOP_ATTN = 1, MOP_RESID = 2, MOP_SWIGLU = 3, MOP_CLS = 4, MOP_ARGMAX = 5, MOP_PARTIAL = 6 };
+
+struct MegaOp {
+    int kind;
+    int fmt;                 // 0 int4, 1 fp16 weights
+    int pro;                 // 0 plain input, 1 RMSNorm(in, gamma), 2 RMSNorm(embedding row of the token, gamma)
+    int rows, cols, nmat;    // d_in, d_out per matrix, matrices
+    int wsize, zsize, ssize; // per-output sizes (words, words, halves)
+    int units;               // 16-byte vectors per row
+    int kw, groups;          // warps per group, groups per CTA
+    int nch, rwc;            // chunks per tile, rows per chunk
+    int ntiles;
+    int chunk_bytes, woff_z, woff_s;
+    int rot;                 // rotation of the tile -> CTA assignment
+    int pad;
+    QWPtrs mat[3];
+    __half* out[3];
+    float* out_f32;
+    const __half* in;
+    const __half* gamma;
+    const __half* kcache;    // attention: this layer's caches
+    const __half* vcache;
+};
+
+struct MegaParams {
+    const MegaOp* ops;
+    int nops;
+    unsigned int* done;        // [nops] arrivals, monotonically increasing over tokens
+    DeviceStatus* status;
+    const float2* rope_table;
+    const __half* embed;
+    __half* x;
+    int* tokens;
+    const __half* logits;
+    int pos, next_pos, write_token;
+    unsigned int seq_no;       // 1, 2, 3, ... : arrivals expected on a counter = seq_no * gridDim.x
+    int dim, head_size, heads_local, kv_row_stride, vocab;
+    float eps, scale;
+    int nstage, slot_bytes, att_cap;
+};
+
+constexpr int kMegaConsumerWarps = 20;
+constexpr int kMegaFinalWarps = 2;
+constexpr int kMegaWarps = kMegaConsumerWarps + 1 + kMegaFinalWarps;
+constexpr int kMegaThreads = kMegaWarps * 32;
+constexpr int kMegaMaxStages = 12;
+constexpr int kMegaRedSlots = 8;
+constexpr int kMegaMaxRows = 8;       // rows per tile
+constexpr int kMegaMaxGroups = 5;
+constexpr uint32_t kBarCount = 32;    // fixed arrival count of the consumer-side mbarriers (see arrive_n)
+
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v)
+{
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+struct MegaChunk {
+    int m, row0, nrows;
+};
+
+// arrivals one CTA makes on an operator's counter: every finalizer warp for weight operators, one thread otherwise
+__host__ __device__ __forceinline__ unsigned int mega_arrivals(const MegaOp& op) { return op.ntiles > 0 ? (unsigned int)kMegaFinalWarps : 1u; }
+
+__device__ __forceinline__ MegaChunk mega_chunk(const MegaOp& op, int head_size, int tile, int c)
+{
+    MegaChunk k;
+    if (op.kind == MOP_SWIGLU) {
+        k.m = c;  // chunk 0 = gate rows, chunk 1 = the same rows of up
+        k.row0 = tile * op.rwc;
+    } else if (op.kind == MOP_QKV) {
+        const int half = head_size >> 1;
+        const int ppm = (op.cols >> 1) / op.rwc;   // pairs per matrix
+        k.m = tile / ppm;
+        const int pp = tile - k.m * ppm;
+        const int pph = half / op.rwc;
+        const int head = pp / pph;
+        k.row0 = head * head_size + (pp - head * pph) * op.rwc + c * half;  // rotate-half partners share a tile
+    } else {
+        k.m = 0;
+        k.row0 = (tile * op.nch + c) * op.rwc;
+    }
+    int n = op.cols - k.row0;
+    n = n < 0 ? 0 : (n > op.rwc ? op.rwc : n);
+    k.nrows = (k.m < op.nmat) ? n : 0;
+    return k;
+}
+
+// Device-wide dependency: waits until `counter` has collected `expected` arrivals (bounded).
+__device__ __forceinline__ void mega_wait_counter(const unsigned int* counter, unsigned int expected, volatile unsigned int* abort_flag,
+                                                  DeviceStatus* status, unsigned int code, int op_index)
+{
+    for (uint32_t i = 0; i < (kSpinLimit >> 2); ++i) {
+        if ((int)(ld_acquire_gpu(counter) - expected) >= 0) return;
+        if ((i & 255u) == 255u && (*abort_flag || ld_acquire_gpu(&status->error))) { *abort_flag = 1; return; }
+        __nanosleep(20);
+    }
+    *abort_flag = 1;
+    atomicExch(&status->error, code);
+    status->detail = (unsigned int)op_index;
+}
+
+template <int NX>
+__device__ __forceinline__ void mega_load_slice(const __half* src, int rows, int e0, uint32_t (&xr)[NX / 2])
+{
+#pragma unroll
+    for (int v = 0; v < NX / 8; ++v) {
+        const int e = e0 + v * 8;
+        uint4 t = make_uint4(0, 0, 0, 0);
+        if (e + 8 <= rows) t = *reinterpret_cast<const uint4*>(src + e);
+        xr[v * 4 + 0] = t.x; xr[v * 4 + 1] = t.y; xr[v * 4 + 2] = t.z; xr[v * 4 + 3] = t.w;
+    }
+}
+
+// RMSNorm of a slice held in registers (native/rmsnorm_kernel.cu:12-35); `tot` is the sum of squares of the vector.
+template <int NX>
+__device__ __forceinline__ void mega_norm_slice(const __half* gamma, int rows, int e0, float tot, float eps, uint32_t (&xr)[NX / 2])
+{
+    const float rms = 1.0f / sqrtf(tot / (float)rows + eps);
+#pragma unroll
+    for (int v = 0; v < NX / 8; ++v) {
+        const int e = e0 + v * 8;
+        if (e + 8 > rows) continue;
+        const uint4 t = *reinterpret_cast<const uint4*>(gamma + e);
+        const uint32_t g4[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t xv = xr[v * 4 + i];
+            const float lo = rms * half_bits_to_float(lo16(g4[i])) * half_bits_to_float(lo16(xv));
+            const float hi = rms * half_bits_to_float(hi16(g4[i])) * half_bits_to_float(hi16(xv));
+            xr[v * 4 + i] = (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+        }
+    }
+}
+
+template <int NX>
+__device__ __forceinline__ float slice_sumsq(const uint32_t (&xr)[NX / 2])
+{
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NX / 2; ++i) {
+        const float a = half_bits_to_float(lo16(xr[i])), b = half_bits_to_float(hi16(xr[i]));
+        ss = fmaf(a, a, ss);
+        ss = fmaf(b, b, ss);
+    }
+    return warp_sum(ss);
+}
+
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const MegaParams p)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];   // [ring: nstage * slot_bytes][attention scores: att_cap floats]
+    __shared__ __align__(8) uint64_t full_bar[kMegaMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMegaMaxStages];
+    __shared__ __align__(8) uint64_t done_bar[kMegaRedSlots];
+    __shared__ __align__(8) uint64_t free_bar[kMegaRedSlots];
+    __shared__ float s_red[kMegaRedSlots][kMaxKW][kMegaMaxRows];
+    __shared__ float s_part[kMegaMaxGroups][kMaxKW];
+    __shared__ float s_att_acc[kMegaConsumerWarps][kHeadMax];
+    __shared__ float s_att_tmp[kMegaConsumerWarps];
+    __shared__ float s_best_v[kMegaConsumerWarps];
+    __shared__ int s_best_i[kMegaConsumerWarps];
+    __shared__ unsigned int s_abort;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int ncta = gridDim.x;
+    const int cta = blockIdx.x;
+    const unsigned int expected = p.seq_no * (unsigned int)ncta;
+    constexpr int kConsThreads = kMegaConsumerWarps * 32;
+
+    if (tid == 0) {
+        for (int s = 0; s < p.nstage; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kBarCount);
+        }
+        for (int s = 0; s < kMegaRedSlots; ++s) {
+            mbar_init(&done_bar[s], kBarCount);
+            mbar_init(&free_bar[s], 1);
+        }
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // tiles of operator `op` owned by this CTA: first + i * ncta, i < count
+    auto my_first = [&](const MegaOp& op) { int f = cta - op.rot; f %= ncta; return f < 0 ? f + ncta : f; };
+    auto my_count = [&](const MegaOp& op, int first) { return op.ntiles > first ? (op.ntiles - 1 - first) / ncta + 1 : 0; };
+
+    if (warp == kMegaConsumerWarps) {
+        // ================= producer =====================================================================
+        const uint64_t pol = policy_evict_first();
+        int n = 0;  // running tile counter of this CTA across operators -> ring slot
+        for (int k = 0; k < p.nops; ++k) {
+            const MegaOp op = p.ops[k];
+            if (op.ntiles == 0) continue;
+            const int first = my_first(op), cnt = my_count(op, first);
+            for (int i = 0; i < cnt; ++i, ++n) {
+                const int tile = first + i * ncta;
+                const int st = n % p.nstage;
+                if (n >= p.nstage) {
+                    if (lane == 0) wait_or_abort(&empty_bar[st], ((n / p.nstage) - 1) & 1, &s_abort, p.status, 1u, k);
+                    __syncwarp();
+                }
+                unsigned char* sbase = smem_raw + (size_t)st * p.slot_bytes;
+                MegaChunk c{0, 0, 0};
+                if (lane < op.nch) c = mega_chunk(op, p.head_size, tile, lane);
+                const QWPtrs q = op.mat[c.m < op.nmat ? c.m : 0];
+                const uint32_t* gw = q.w + (size_t)c.row0 * op.wsize;
+                const uint32_t bw = (uint32_t)c.nrows * op.wsize * 4u;
+                const uint32_t* gz = nullptr;
+                const __half* gs = nullptr;
+                uint32_t bz = 0, bs = 0;
+                if (op.fmt == 0) {
+                    gz = q.z + (size_t)c.row0 * op.zsize;
+                    gs = q.s + (size_t)c.row0 * op.ssize;
+                    bz = (uint32_t)c.nrows * op.zsize * 4u;
+                    bs = (uint32_t)c.nrows * op.ssize * 2u;
+                }
+                const bool live = c.nrows > 0;
+                uint32_t tx = live ? (bw + bz + bs) : 0u;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[st], tx);
+                __syncwarp();
+                if (live) {
+                    unsigned char* cb = sbase + (size_t)lane * op.chunk_bytes;
+                    bulk_g2s(cb, gw, bw, &full_bar[st], pol);
+                    if (op.fmt == 0) {
+                        bulk_g2s(cb + op.woff_z, gz, bz, &full_bar[st], pol);
+                        bulk_g2s(cb + op.woff_s, gs, bs, &full_bar[st], pol);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    if (warp > kMegaConsumerWarps) {
+        // ================= finalizers: fixed-order sum over k-warps + operator tail ========================
+        const int fw = warp - kMegaConsumerWarps - 1;
+        int n = 0;
+        for (int k = 0; k < p.nops; ++k) {
+            const MegaOp op = p.ops[k];
+            if (op.ntiles == 0) continue;   // attention / argmax are published by the consumers
+            const int first = my_first(op), cnt = my_count(op, first);
+            for (int i = 0; i < cnt; ++i, ++n) {
+                if ((n % kMegaFinalWarps) != fw) continue;
+                const int tile = first + i * ncta;
+                const int slot = n % kMegaRedSlots;
+                const float* red = &s_red[slot][0][0];
+                if (op.kind == MOP_SWIGLU || op.kind == MOP_QKV) {
+                    const bool mine = lane < op.rwc;
+                    MegaChunk ca{0, 0, 0}, cb{0, 0, 0};
+                    if (mine) { ca = mega_chunk(op, p.head_size, tile, 0); cb = mega_chunk(op, p.head_size, tile, 1); }
+                    const int r = lane;
+                    float2 cs = make_float2(1.f, 0.f);
+                    if (op.kind == MOP_QKV && mine && r < ca.nrows && ca.m < 2)
+                        cs = p.rope_table[(size_t)p.pos * (p.head_size >> 1) + (ca.row0 + r) % p.head_size];
+                    wait_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1, &s_abort, p.status, 3u, k);
+                    if (mine && r < ca.nrows) {
+                        float sa = 0.f, sb = 0.f;
+                        for (int w = 0; w < op.kw; ++w) {
+                            sa += red[w * kMegaMaxRows + r];
+                            sb += red[w * kMegaMaxRows + op.rwc + r];
+                        }
+                        if (op.kind == MOP_SWIGLU) {
+                            float val = sa;                       // native/mat_vec_kernel.cu:218-222
+                            val *= 1.0f / (1.0f + expf(-val));
+                            val *= sb;
+                            op.out[0][ca.row0 + r] = __float2half_rn(val);
+                        } else {
+                            __half* o = op.out[ca.m];
+                            if (ca.m > 0) o += (long long)p.pos * p.kv_row_stride;
+                            if (ca.m < 2) {
+                                // fp16 store of the mat-vec (native/mat_vec_kernel.cu:175), then RoPE on the rounded
+                                // values (native/rope_kernel.cu:15-25)
+                                const float a0 = __half2float(__float2half_rn(sa));
+                                const float b0 = __half2float(__float2half_rn(sb));
+                                o[ca.row0 + r] = __float2half_rn(a0 * cs.x - b0 * cs.y);
+                                o[cb.row0 + r] = __float2half_rn(a0 * cs.y + b0 * cs.x);
+                            } else {
+                                o[ca.row0 + r] = __float2half_rn(sa);
+                                o[cb.row0 + r] = __float2half_rn(sb);
+                            }
+                        }
+                    }
+                } else {
+                    const int nrow = op.nch * op.rwc;
+                    const int ch = lane / op.rwc, r = lane - ch * op.rwc;
+                    MegaChunk c{0, 0, 0};
+                    if (lane < nrow) c = mega_chunk(op, p.head_size, tile, ch);
+                    const bool mine = lane < nrow && r < c.nrows;
+                    const int row = c.row0 + r;
+                    wait_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1, &s_abort, p.status, 3u, k);
+                    if (mine) {
+                        float sum = 0.f;
+                        for (int w = 0; w < op.kw; ++w) sum += red[w * kMegaMaxRows + ch * op.rwc + r];
+                        // the residual value was fetched by the consumers (they hold the operator's dependency) and
+                        // travels in the extra k-row of the partial slot
+                        if (op.kind == MOP_RESID)
+                            op.out[0][row] = __float2half_rn(sum + red[op.kw * kMegaMaxRows + ch * op.rwc + r]);  // native/mat_vec_kernel.cu:154-156
+                        else if (op.kind == MOP_PARTIAL) op.out_f32[row] = sum;
+                        else op.out[0][row] = __float2half_rn(sum);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&free_bar[slot]);
+            }
+            // this CTA's share of operator k is written: publish it (each finalizer warp fences its own stores)
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) red_release_gpu_add(&p.done[k], 1u);
+        }
+        return;
+    }
+
+    // ================= consumers =========================================================================
+    int n_base = 0;  // running tile counter at the start of the current operator
+    for (int k = 0; k < p.nops; ++k) {
+        const MegaOp op = p.ops[k];
+
+        // ---- dependency: the previous operator's output is complete everywhere -----------------------------
+        if (k > 0) {
+            if (tid == 0) mega_wait_counter(&p.done[k - 1], expected * mega_arrivals(p.ops[k - 1]), &s_abort, p.status, 5u, k);
+            named_bar_sync(1, kConsThreads);
+        }
+
+        if (op.kind == MOP_ATTN) {
+            // ---- attention of head `cta` (reference: mat_vec_strided / softmax / vec_mat kernels) -------------
+            if (cta < p.heads_local) {
+                float* s_sc = reinterpret_cast<float*>(smem_raw + (size_t)p.nstage * p.slot_bytes);
+                const int head = cta;
+                const int nseq = p.pos + 1;
+                const __half* kh = op.kcache + (size_t)head * p.head_size;
+                const __half* vh = op.vcache + (size_t)head * p.head_size;
+                const uint2 qv = *reinterpret_cast<const uint2*>(op.in + (size_t)head * p.head_size + lane * 4);
+                float mx = -INFINITY;
+                for (int t = warp; t < nseq; t += kMegaConsumerWarps) {
+                    const uint2 kv = *reinterpret_cast<const uint2*>(kh + (size_t)t * p.kv_row_stride + lane * 4);
+                    float s = 0.f;
+                    s = fma_f16_f32(lo16(kv.x), lo16(qv.x), s);
+                    s = fma_f16_f32(hi16(kv.x), hi16(qv.x), s);
+                    s = fma_f16_f32(lo16(kv.y), lo16(qv.y), s);
+                    s = fma_f16_f32(hi16(kv.y), hi16(qv.y), s);
+                    s = warp_sum(s);
+                    const float sr = __half2float(__float2half_rn(s * p.scale));   // native/mat_vec_kernel.cu:72-73
+                    if (lane == 0) s_sc[t] = sr;
+                    mx = fmaxf(mx, sr);
+                }
+                if (lane == 0) s_att_tmp[warp] = mx;
+                named_bar_sync(1, kConsThreads);
+                mx = s_att_tmp[0];
+#pragma unroll
+                for (int w = 1; w < kMegaConsumerWarps; ++w) mx = fmaxf(mx, s_att_tmp[w]);
+                named_bar_sync(1, kConsThreads);
+                float sum = 0.f;
+                for (int i = tid; i < nseq; i += kConsThreads) {
+                    const float e = expf(s_sc[i] - mx);                          // native/softmax_kernel.cu:37
+                    s_sc[i] = e;
+                    sum += e;
+                }
+                sum = warp_sum(sum);
+                if (lane == 0) s_att_tmp[warp] = sum;
+                named_bar_sync(1, kConsThreads);
+                float total = 0.f;
+#pragma unroll
+                for (int w = 0; w < kMegaConsumerWarps; ++w) total += s_att_tmp[w];
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int t = warp; t < nseq; t += kMegaConsumerWarps) {
+                    const unsigned short pr = __half_as_ushort(__float2half_rn(s_sc[t] / total));   // native/softmax_kernel.cu:46
+                    const uint2 vv = *reinterpret_cast<const uint2*>(vh + (size_t)t * p.kv_row_stride + lane * 4);
+                    acc[0] = fma_f16_f32(pr, lo16(vv.x), acc[0]);
+                    acc[1] = fma_f16_f32(pr, hi16(vv.x), acc[1]);
+                    acc[2] = fma_f16_f32(pr, lo16(vv.y), acc[2]);
+                    acc[3] = fma_f16_f32(pr, hi16(vv.y), acc[3]);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s_att_acc[warp][lane * 4 + e] = acc[e];
+                named_bar_sync(1, kConsThreads);
+                if (tid < p.head_size) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kMegaConsumerWarps; ++w) s += s_att_acc[w][tid];
+                    op.out[0][(size_t)head * p.head_size + tid] = __float2half_rn(s);   // native/vec_mat_kernel.cu:41
+                }
+                __threadfence();
+                named_bar_sync(1, kConsThreads);
+            }
+            if (tid == 0) red_release_gpu_add(&p.done[k], 1u);
+            continue;
+        }
+
+        if (op.kind == MOP_ARGMAX) {
+            // ---- greedy sample on CTA 0 (native/argmax_kernel.cu:8-46, lowest index on ties) --------------------
+            if (cta == 0) {
+                float best = -INFINITY;
+                int best_i = 0x7fffffff;
+                for (int i = tid; i < p.vocab; i += kConsThreads) {
+                    const float v = __half2float(p.logits[i]);
+                    if (v > best) { best = v; best_i = i; }
+                }
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+                    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+                }
+                if (lane == 0) { s_best_v[warp] = best; s_best_i[warp] = best_i; }
+                named_bar_sync(1, kConsThreads);
+                if (tid == 0) {
+                    for (int w = 1; w < kMegaConsumerWarps; ++w)
+                        if (s_best_v[w] > best || (s_best_v[w] == best && s_best_i[w] < best_i)) { best = s_best_v[w]; best_i = s_best_i[w]; }
+                    if (p.write_token) p.tokens[p.next_pos] = (best_i == 0x7fffffff) ? 0 : best_i;
+                }
+            }
+            if (tid == 0) red_release_gpu_add(&p.done[k], 1u);
+            continue;
+        }
+
+        // ---- weight operators ------------------------------------------------------------------------------
+        const int first = my_first(op), cnt = my_count(op, first);
+        const int group = warp / op.kw;
+        const int kw_id = warp - group * op.kw;
+        const bool in_group = group < op.groups;
+        const int u = kw_id * 32 + lane;
+        const bool active = in_group && u < op.units;
+        const bool is_int4 = op.fmt == 0;
+        const int nx = is_int4 ? 32 : 8;
+        const int e0 = u * nx;
+
+        // input slice -> registers (xp: paired for the nibble masks when int4)
+        uint32_t xp[16];
+        float nlo = 0.f, nhi = 0.f, c1 = 0.f;
+        {
+            const __half* src = op.in;
+            if (op.pro == 2) src = p.embed + (size_t)p.tokens[p.pos] * op.rows;   // native/embedding_kernel.cu:6-12
+            uint32_t xr[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) xr[i] = 0u;
+            if (active) {
+                if (is_int4) {
+                    mega_load_slice<32>(src, op.rows, e0, xr);
+                } else {
+                    uint32_t t4[4];
+                    mega_load_slice<8>(src, op.rows, e0, t4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) xr[i] = t4[i];
+                }
+            }
+            if (op.pro == 2 && cta == 0 && group == 0 && active) {
+                // the residual stream starts as the embedding row: one CTA stores it for the later residual adds
+                uint4* dst = reinterpret_cast<uint4*>(p.x + e0);
+                if (is_int4) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) dst[v] = make_uint4(xr[4 * v], xr[4 * v + 1], xr[4 * v + 2], xr[4 * v + 3]);
+                } else {
+                    dst[0] = make_uint4(xr[0], xr[1], xr[2], xr[3]);
+                }
+            }
+            if (op.pro != 0) {
+                float ss = 0.f;
+                if (is_int4) ss = slice_sumsq<32>(xr);
+                else { uint32_t t4[4] = {xr[0], xr[1], xr[2], xr[3]}; ss = slice_sumsq<8>(t4); }
+                if (in_group && lane == 0) s_part[group][kw_id] = ss;
+                named_bar_sync(1, kConsThreads);
+                float tot = 0.f;
+                const int g = in_group ? group : 0;
+                for (int w = 0; w < op.kw; ++w) tot += s_part[g][w];
+                if (active) {
+                    if (is_int4) mega_norm_slice<32>(op.gamma, op.rows, e0, tot, p.eps, xr);
+                    else { uint32_t t4[4] = {xr[0], xr[1], xr[2], xr[3]}; mega_norm_slice<8>(op.gamma, op.rows, e0, tot, p.eps, t4);
+                           xr[0] = t4[0]; xr[1] = t4[1]; xr[2] = t4[2]; xr[3] = t4[3]; }
+                }
+                named_bar_sync(1, kConsThreads);   // s_part is reused by the next operator
+            }
+            if (is_int4) {
+                float se = 0.f, so = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t h01 = xr[4 * j], h23 = xr[4 * j + 1], h45 = xr[4 * j + 2], h67 = xr[4 * j + 3];
+                    xp[4 * j + 0] = __byte_perm(h01, h45, 0x5410);
+                    xp[4 * j + 1] = __byte_perm(h01, h45, 0x7632);
+                    xp[4 * j + 2] = __byte_perm(h23, h67, 0x5410);
+                    xp[4 * j + 3] = __byte_perm(h23, h67, 0x7632);
+                    se += half_bits_to_float(lo16(h01)) + half_bits_to_float(lo16(h23)) + half_bits_to_float(lo16(h45)) +
+                          half_bits_to_float(lo16(h67));
+                    so += half_bits_to_float(hi16(h01)) + half_bits_to_float(hi16(h23)) + half_bits_to_float(hi16(h45)) +
+                          half_bits_to_float(hi16(h67));
+                }
+                nlo = -1024.0f * se;
+                nhi = -1024.0f * so;
+                c1 = se + so;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) xp[i] = xr[i];
+            }
+        }
+
+        const int g = u >> 2;
+        const int zshift = (g & 7) * 4;
+        const uint32_t w_off = (uint32_t)(active ? u : 0) * 16u;
+        const uint32_t z_off = op.woff_z + (uint32_t)(active ? (g >> 3) : 0) * 4u;
+        const uint32_t s_off = op.woff_s + (uint32_t)(active ? g : 0) * 2u;
+        const uint32_t w_row = (uint32_t)op.wsize * 4u, z_row = (uint32_t)op.zsize * 4u, s_row = (uint32_t)op.ssize * 2u;
+        const uint32_t ring = smem_u32(smem_raw);
+        // arrival weights: the fixed barrier count is met by (kw - 1) single arrivals + one weighted arrival per tile
+        const uint32_t my_arrive = (kw_id == 0) ? (kBarCount - (uint32_t)op.kw + 1u) : 1u;
+
+        for (int i = 0; i < cnt; ++i) {
+            const int n = n_base + i;
+            const int owner = i % op.groups;
+            if (!in_group || owner != group) continue;   // another group's tile (idle warps take none)
+            const int st = n % p.nstage;
+            wait_or_abort(&full_bar[st], (n / p.nstage) & 1, &s_abort, p.status, 2u, k);
+            const int slot = n % kMegaRedSlots;
+            bool slot_ready = n < kMegaRedSlots;
+            float resid[2] = {0.f, 0.f};
+            if (op.kind == MOP_RESID && kw_id == 0 && (lane & 7) == 0 && (lane >> 3) < op.rwc) {
+                const int tile = first + i * ncta;
+                for (int c = 0; c < op.nch; ++c) {
+                    const int row = (tile * op.nch + c) * op.rwc + (lane >> 3);
+                    if (row < op.cols) resid[c] = __half2float(op.out[0][row]);
+                }
+            }
+            for (int c = 0; c < op.nch; ++c) {
+                const uint32_t cb = ring + (uint32_t)st * p.slot_bytes + (uint32_t)c * op.chunk_bytes;
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (is_int4) {
+                    uint4 wv[4];
+                    uint32_t zw[4];
+                    unsigned short sc[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(wv[r].x), "=r"(wv[r].y), "=r"(wv[r].z), "=r"(wv[r].w)
+                                     : "r"(cb + w_off + r * w_row));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cb + z_off + r * z_row));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cb + s_off + r * s_row));
+                    }
+                    float alo[4], ahi[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        alo[r] = nlo;
+                        ahi[r] = nhi;
+                        word_dot(wv[r].x, xp + 0, alo[r], ahi[r]);
+                        word_dot(wv[r].y, xp + 4, alo[r], ahi[r]);
+                        word_dot(wv[r].z, xp + 8, alo[r], ahi[r]);
+                        word_dot(wv[r].w, xp + 12, alo[r], ahi[r]);
+                    }
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float zf = (float)((zw[r] >> zshift) & 0xFu);
+                        const float t = fmaf(ahi[r], 0.0625f, alo[r]);
+                        const float res = half_bits_to_float(sc[r]) * fmaf(-zf, c1, t);
+                        v[r] = active ? res : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (r < op.rwc) {
+                            uint4 wv;
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
+                                         : "r"(cb + w_off + r * w_row));
+                            float a0 = 0.f, a1 = 0.f;
+                            a0 = fma_f16_f32(lo16(wv.x), lo16(xp[0]), a0);
+                            a1 = fma_f16_f32(hi16(wv.x), hi16(xp[0]), a1);
+                            a0 = fma_f16_f32(lo16(wv.y), lo16(xp[1]), a0);
+                            a1 = fma_f16_f32(hi16(wv.y), hi16(xp[1]), a1);
+                            a0 = fma_f16_f32(lo16(wv.z), lo16(xp[2]), a0);
+                            a1 = fma_f16_f32(hi16(wv.z), hi16(xp[2]), a1);
+                            a0 = fma_f16_f32(lo16(wv.w), lo16(xp[3]), a0);
+                            a1 = fma_f16_f32(hi16(wv.w), hi16(xp[3]), a1);
+                            v[r] = active ? (a0 + a1) : 0.f;
+                        }
+                    }
+                }
+                if (c == op.nch - 1) {
+                    // last read of the stage by this warp: hand it back to the producer
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_n(&empty_bar[st], my_arrive);
+                }
+                transpose_reduce<4>(v, lane);
+                if (!slot_ready) {
+                    wait_or_abort(&free_bar[slot], ((n / kMegaRedSlots) - 1) & 1, &s_abort, p.status, 4u, k);
+                    slot_ready = true;
+                }
+                if ((lane & 7) == 0 && (lane >> 3) < op.rwc) s_red[slot][kw_id][c * op.rwc + (lane >> 3)] = v[0];
+                if (op.kind == MOP_RESID && kw_id == 0 && (lane & 7) == 0 && (lane >> 3) < op.rwc)
+                    s_red[slot][op.kw][c * op.rwc + (lane >> 3)] = resid[c];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_n(&done_bar[slot], my_arrive);
+        }
+        n_base += cnt;
+    }
+}
+
+}  // namespace ml2

@@ -25,6 +25,7 @@
 
 #include "attention.cuh"
 #include "host_common.hpp"
+#include "megakernel.cuh"
 #include "small_ops.cuh"
 #include "stream_matvec.cuh"
 
@@ -169,6 +170,13 @@ struct Model {
     bool use_pdl = true;
     long long launches_per_token = 0;
     std::vector<void*> owned;
+    // persistent per-token kernel (single launch per token)
+    bool use_mega = true;
+    bool mega_built = false, mega_ok = false;
+    MegaOp* mega_ops = nullptr;
+    unsigned int* mega_done = nullptr;
+    int mega_nops = 0, mega_nstage = 0, mega_slot = 0, mega_att_bytes = 0, mega_smem = 0, mega_grid = 0;
+    unsigned int mega_seq = 0;
 };
 
 #define ML2_CUDA(call)                                                                       \
@@ -381,6 +389,155 @@ static double qweight_bytes(int rows, int cols)
     return (double)cols * (ws * 4.0 + zs * 4.0 + ss * 2.0);
 }
 
+// ---- persistent per-token kernel: operator list and launch ------------------------------------------------------
+static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols)
+{
+    op.fmt = fmt;
+    op.rows = rows;
+    op.cols = cols;
+    if (fmt == 0) {
+        op.ssize = ceil_div(rows, kGroup);
+        op.wsize = ceil_div(rows, 32) * 4;
+        op.zsize = ceil_div(op.ssize, 8);
+        if ((rows % 32) || (op.ssize & 1)) return false;   // 4-row runs of scales must be 16-byte multiples
+        op.rwc = 4;
+    } else {
+        if (rows % 8) return false;
+        op.wsize = rows / 2;
+        op.zsize = op.ssize = 0;
+        op.rwc = (rows * 2 * 4 <= 24 * 1024) ? 4 : 2;
+    }
+    if (cols % op.rwc) return false;
+    op.units = op.wsize / 4;
+    op.kw = ceil_div(op.units, 32);
+    if (op.kw > kMegaConsumerWarps) return false;
+    op.groups = std::min(kMegaMaxGroups, kMegaConsumerWarps / op.kw);
+    auto a16 = [](int b) { return (b + 15) & ~15; };
+    op.woff_z = a16(op.rwc * op.wsize * 4);
+    op.woff_s = op.woff_z + a16(op.rwc * op.zsize * 4);
+    op.chunk_bytes = op.woff_s + a16(op.rwc * op.ssize * 2);
+    return true;
+}
+
+static int build_mega(Model* m)
+{
+    m->mega_built = true;
+    m->mega_ok = false;
+    if (!m->use_mega || m->tp != 1) return ML2_OK;
+    const ml2_config& c = m->cfg;
+    const int dim = c.dim, hs = m->head_size;
+    if (m->heads_local > m->ctx->sm_count || (hs / 2) % 4) return ML2_OK;
+    std::vector<MegaOp> ops;
+    const size_t kv_layer = (size_t)c.seq_len * m->dim_local;
+    long long tiles_before = 0;
+    auto push = [&](MegaOp& op) {
+        op.rot = (int)(tiles_before % m->ctx->sm_count);
+        tiles_before += op.ntiles;
+        ops.push_back(op);
+    };
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerW& L = m->layers[l];
+        __half* kc = m->key_cache + (size_t)l * kv_layer;
+        __half* vc = m->value_cache + (size_t)l * kv_layer;
+        MegaOp q{};
+        q.kind = MOP_QKV; q.pro = (l == 0) ? 2 : 1; q.nmat = 3; q.nch = 2;
+        if (!mega_plan_op(q, 0, dim, m->dim_local)) return ML2_OK;
+        q.ntiles = 3 * (m->dim_local / 2 / q.rwc);
+        q.mat[0] = qwp(L.q); q.mat[1] = qwp(L.k); q.mat[2] = qwp(L.v);
+        q.out[0] = m->q; q.out[1] = kc; q.out[2] = vc;
+        q.in = m->x; q.gamma = L.rms_att;
+        push(q);
+        MegaOp a{};
+        a.kind = MOP_ATTN; a.in = m->q; a.out[0] = m->xb; a.kcache = kc; a.vcache = vc; a.ntiles = 0;
+        push(a);
+        MegaOp o{};
+        o.kind = MOP_RESID; o.pro = 0; o.nmat = 1; o.nch = 1;
+        if (!mega_plan_op(o, 0, m->dim_local, dim)) return ML2_OK;
+        o.ntiles = ceil_div(dim, o.rwc);
+        o.mat[0] = qwp(L.o); o.out[0] = m->x; o.in = m->xb;
+        push(o);
+        MegaOp g{};
+        g.kind = MOP_SWIGLU; g.pro = 1; g.nmat = 2; g.nch = 2;
+        if (!mega_plan_op(g, 0, dim, m->hidden_local)) return ML2_OK;
+        g.ntiles = ceil_div(m->hidden_local, g.rwc);
+        g.mat[0] = qwp(L.gate); g.mat[1] = qwp(L.up); g.out[0] = m->h; g.in = m->x; g.gamma = L.rms_ffn;
+        push(g);
+        MegaOp d{};
+        d.kind = MOP_RESID; d.pro = 0; d.nmat = 1; d.nch = 1;
+        if (!mega_plan_op(d, 0, m->hidden_local, dim)) return ML2_OK;
+        d.ntiles = ceil_div(dim, d.rwc);
+        d.mat[0] = qwp(L.down); d.out[0] = m->x; d.in = m->h;
+        push(d);
+    }
+    MegaOp cl{};
+    cl.kind = MOP_CLS; cl.pro = 1; cl.nmat = 1; cl.nch = 1;
+    if (!mega_plan_op(cl, 1, dim, m->vocab_local)) return ML2_OK;
+    cl.ntiles = ceil_div(m->vocab_local, cl.rwc);
+    cl.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
+    cl.out[0] = m->logits; cl.in = m->x; cl.gamma = m->rms_final;
+    push(cl);
+    MegaOp am{};
+    am.kind = MOP_ARGMAX; am.ntiles = 0;
+    push(am);
+
+    int slot = 0;
+    for (const MegaOp& op : ops)
+        if (op.ntiles > 0) slot = std::max(slot, op.nch * op.chunk_bytes);
+    slot = (slot + 127) & ~127;
+    const int att_bytes = ((c.seq_len * 4) + 127) & ~127;
+    const int budget = 200 * 1024;
+    int nstage = (budget - att_bytes) / slot;
+    if (nstage > kMegaMaxStages) nstage = kMegaMaxStages;
+    if (nstage < 2) return ML2_OK;
+    m->mega_slot = slot;
+    m->mega_nstage = nstage;
+    m->mega_att_bytes = att_bytes;
+    m->mega_smem = nstage * slot + att_bytes;
+    m->mega_nops = (int)ops.size();
+    m->mega_grid = m->ctx->sm_count;
+    ML2_CUDA(cudaFuncSetAttribute(decode_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, m->mega_smem));
+    int per_sm = 0;
+    ML2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_token_kernel, kMegaThreads, m->mega_smem));
+    if (per_sm < 1) return ML2_OK;
+    if (m->mega_ops) { cudaFree(m->mega_ops); m->mega_ops = nullptr; }
+    ML2_CUDA(cudaMalloc(&m->mega_ops, ops.size() * sizeof(MegaOp)));
+    ML2_CUDA(cudaMemcpyAsync(m->mega_ops, ops.data(), ops.size() * sizeof(MegaOp), cudaMemcpyHostToDevice, m->stream));
+    if (!m->mega_done) {
+        ML2_CUDA(cudaMalloc(&m->mega_done, ops.size() * sizeof(unsigned int)));
+    }
+    ML2_CUDA(cudaMemsetAsync(m->mega_done, 0, ops.size() * sizeof(unsigned int), m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    m->mega_seq = 0;
+    m->mega_ok = true;
+    return ML2_OK;
+}
+
+static int forward_mega(Model* m, int pos, int next_pos, int write_token)
+{
+    MegaParams prm{};
+    prm.ops = m->mega_ops;
+    prm.nops = m->mega_nops;
+    prm.done = m->mega_done;
+    prm.status = m->ctx->status_dev;
+    prm.rope_table = m->rope_table;
+    prm.embed = m->embed;
+    prm.x = m->x;
+    prm.tokens = m->tokens;
+    prm.logits = m->logits;
+    prm.pos = pos; prm.next_pos = next_pos; prm.write_token = write_token;
+    prm.seq_no = ++m->mega_seq;
+    prm.dim = m->cfg.dim; prm.head_size = m->head_size; prm.heads_local = m->heads_local;
+    prm.kv_row_stride = m->dim_local; prm.vocab = m->cfg.vocab_size;
+    prm.eps = m->eps; prm.scale = 1.0f / sqrtf((float)m->head_size);
+    prm.nstage = m->mega_nstage; prm.slot_bytes = m->mega_slot; prm.att_cap = m->cfg.seq_len;
+    void* args[] = {&prm};
+    ML2_CUDA(cudaLaunchCooperativeKernel((const void*)decode_token_kernel, dim3(m->mega_grid), dim3(kMegaThreads), args,
+                                         (size_t)m->mega_smem, m->stream));
+    ++m->ctx->launches;
+    m->launches_per_token = 1;
+    return ML2_OK;
+}
+
 static int check_bound(Model* m)
 {
     if (!m->embed || !m->classifier || !m->rms_final) return fail(ML2_E_STATE, "model: globals are not bound");
@@ -443,6 +600,8 @@ int ml2_model_create(ml2_ctx* h, const ml2_config* cfg, int tp_size, int tp_rank
     m->layers.resize(c.n_layers);
     const char* eg = getenv("ML2_NO_GRAPH");
     m->use_graph = !(eg && *eg == '1');
+    const char* em = getenv("ML2_NO_MEGA");
+    m->use_mega = !(em && *em == '1');
     const char* ep = getenv("ML2_NO_PDL");
     m->use_pdl = !(ep && *ep == '1');
     ML2_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
@@ -485,6 +644,8 @@ int ml2_model_destroy(ml2_model* h)
     if (m->exec) cudaGraphExecDestroy(m->exec);
     if (m->graph) cudaGraphDestroy(m->graph);
     if (m->comm) g_nccl.CommDestroy(m->comm);
+    if (m->mega_ops) cudaFree(m->mega_ops);
+    if (m->mega_done) cudaFree(m->mega_done);
     for (void* p : m->owned) cudaFree(p);
     if (m->ctx->stream == m->stream) m->ctx->stream = nullptr;
     cudaStreamDestroy(m->stream);
@@ -538,6 +699,7 @@ int ml2_model_bind_layer(ml2_model* h, int layer, const ml2_layer_weights* w)
     L.rms_att = static_cast<const __half*>(w->rms_attention);
     L.rms_ffn = static_cast<const __half*>(w->rms_feed_forward);
     L.bound = true;
+    m->mega_built = false;
     if (m->exec) { cudaGraphExecDestroy(m->exec); m->exec = nullptr; }
     return ML2_OK;
 }
@@ -570,6 +732,7 @@ int ml2_model_bind_runstate(ml2_model* h, const ml2_runstate* rs)
         if (!p || (reinterpret_cast<uintptr_t>(p) & 15u)) return fail(ML2_E_INVALID, "bind_runstate: buffers must be non-null and 16-byte aligned");
     m->x = (__half*)rs->x; m->xb = (__half*)rs->xb; m->h = (__half*)rs->h; m->q = (__half*)rs->q; m->logits = (__half*)rs->logits;
     m->key_cache = (__half*)rs->key_cache; m->value_cache = (__half*)rs->value_cache; m->tokens = (int*)rs->tokens;
+    m->mega_built = false;
     if (m->exec) { cudaGraphExecDestroy(m->exec); m->exec = nullptr; }
     return ML2_OK;
 }
@@ -593,6 +756,8 @@ int ml2_model_forward(ml2_model* h, int pos, int next_pos, int write_token)
         return fail(ML2_E_INVALID, "forward: pos=%d next_pos=%d outside [0,%d)", pos, next_pos, m->cfg.seq_len);
     Ctx* ctx = m->ctx;
     ctx->stream = m->stream;
+    if (!m->mega_built && (rc = build_mega(m))) return rc;
+    if (m->mega_ok) return forward_mega(m, pos, next_pos, write_token);
     if (!m->use_graph) return enqueue_token(m, pos, next_pos, write_token);
 
     if (!m->exec) {

@@ -53,16 +53,20 @@ def test_synthetic_device_equals_host():
     ctx.close()
 
 
-@pytest.mark.parametrize("no_graph", ["0", "1"])
-def test_greedy_decode_matches_oracle(no_graph):
+@pytest.mark.parametrize("mode", ["persistent", "graph", "eager"])
+def test_greedy_decode_matches_oracle(mode):
+    """The three ways the per-token sequence can run: one persistent kernel, a CUDA graph of per-operator kernels,
+    or those kernels launched eagerly. All must match the oracle."""
     import managedllama2_b200 as ml2
-    os.environ["ML2_NO_GRAPH"] = no_graph
+    env = {"persistent": {}, "graph": {"ML2_NO_MEGA": "1"}, "eager": {"ML2_NO_MEGA": "1", "ML2_NO_GRAPH": "1"}}[mode]
+    os.environ.update(env)
     try:
         cfg = small_config(ml2)
         ctx = ml2.CudaContext(0)
         tr = ml2.Transformer(cfg, ml2.synthetic_weights(ctx, cfg, seed=11), ctx)
     finally:
-        os.environ.pop("ML2_NO_GRAPH", None)
+        for k in env:
+            os.environ.pop(k, None)
     cpu, _ = oracle_model(ml2, cfg, 11)
     rng = np.random.default_rng(3)
     prompt = rng.integers(3, cfg.vocabSize, size=8).astype(np.int32)
@@ -88,7 +92,7 @@ def test_greedy_decode_matches_oracle(no_graph):
                 top2 = np.sort(want)[-2:]
                 assert top2[1] - top2[0] <= 2 * err + 1e-7, (pos, tok, o)
             tokens.append(tok)
-    assert tr.launches_per_token == 5 * cfg.numLayers + 3
+    assert tr.launches_per_token == (1 if mode == "persistent" else 5 * cfg.numLayers + 3)
     err, _ = ctx.status()
     assert err == 0
     tr.close()
