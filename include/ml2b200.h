@@ -201,6 +201,9 @@ int ml2_model_set_tokens(ml2_model* model, const int* tokens_host, int first, in
 int ml2_model_put_token_async(ml2_model* model, int pos, const int* token_pinned_host);
 int ml2_model_read_token(ml2_model* model, int pos, int* token_host);
 int ml2_model_read_logits(ml2_model* model, void* logits_host_f16);
+/* Diagnostics: per-CTA cycle counters of the last persistent-kernel launch (16 values per CTA: total, dependency
+ * waits, ring waits, partial-slot waits, attention, prologue); needs ML2_MEGA_PROF=1 in the environment. */
+int ml2_model_debug_prof(ml2_model* model, long long* out, int n);
 /* The CUDA stream the model launches on (for events or for ordering other work after it). */
 int ml2_model_stream(ml2_model* model, void** cuda_stream);
 /* Times each kernel kind alone over all layers (kinds: 0 qkv, 1 attention, 2 o-proj, 3 gate/up, 4 down,

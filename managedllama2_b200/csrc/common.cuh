@@ -48,6 +48,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is pending:
+// a waiting warp then costs almost no issue slots (used by the roles that are not on the critical path).
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait. Returns false when the limit ran out (caller records the error and leaves).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {

@@ -62,6 +62,8 @@ struct MegaParams {
     int dim, head_size, heads_local, kv_row_stride, vocab;
     float eps, scale;
     int nstage, slot_bytes, att_cap;
+    int debug;                 // bit 0: consumers skip the arithmetic (pipeline probe)
+    long long* prof;           // optional [gridDim.x][64] cycle counters (diagnostics), may be null
 };
 
 constexpr int kMegaConsumerWarps = 20;
@@ -72,7 +74,7 @@ constexpr int kMegaMaxStages = 12;
 constexpr int kMegaRedSlots = 8;
 constexpr int kMegaMaxRows = 8;       // rows per tile
 constexpr int kMegaMaxGroups = 5;
-constexpr uint32_t kBarCount = 32;    // fixed arrival count of the consumer-side mbarriers (see arrive_n)
+constexpr uint32_t kBarCount = 64;    // fixed arrival count of the consumer-side mbarriers (see arrive_n)
 
 __device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n)
 {
@@ -124,10 +126,9 @@ __device__ __forceinline__ MegaChunk mega_chunk(const MegaOp& op, int head_size,
 __device__ __forceinline__ void mega_wait_counter(const unsigned int* counter, unsigned int expected, volatile unsigned int* abort_flag,
                                                   DeviceStatus* status, unsigned int code, int op_index)
 {
-    for (uint32_t i = 0; i < (kSpinLimit >> 2); ++i) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if ((int)(ld_acquire_gpu(counter) - expected) >= 0) return;
         if ((i & 255u) == 255u && (*abort_flag || ld_acquire_gpu(&status->error))) { *abort_flag = 1; return; }
-        __nanosleep(20);
     }
     *abort_flag = 1;
     atomicExch(&status->error, code);
@@ -188,7 +189,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     __shared__ __align__(8) uint64_t done_bar[kMegaRedSlots];
     __shared__ __align__(8) uint64_t free_bar[kMegaRedSlots];
     __shared__ float s_red[kMegaRedSlots][kMaxKW][kMegaMaxRows];
-    __shared__ float s_part[kMegaMaxGroups][kMaxKW];
+    __shared__ float s_part[2][1][kMaxKW];   // per-warp sum-of-squares partials, double-buffered by operator parity
     __shared__ float s_att_acc[kMegaConsumerWarps][kHeadMax];
     __shared__ float s_att_tmp[kMegaConsumerWarps];
     __shared__ float s_best_v[kMegaConsumerWarps];
@@ -224,16 +225,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     if (warp == kMegaConsumerWarps) {
         // ================= producer =====================================================================
         const uint64_t pol = policy_evict_first();
-        int n = 0;  // running tile counter of this CTA across operators -> ring slot
+        // ring position of this CTA's running tile counter, kept without divisions: stage index and use count parity
+        int st = 0;
+        uint32_t ph = 0;      // parity of (uses of this stage so far)
+        bool wrapped = false;
         for (int k = 0; k < p.nops; ++k) {
             const MegaOp op = p.ops[k];
             if (op.ntiles == 0) continue;
             const int first = my_first(op), cnt = my_count(op, first);
-            for (int i = 0; i < cnt; ++i, ++n) {
-                const int tile = first + i * ncta;
-                const int st = n % p.nstage;
-                if (n >= p.nstage) {
-                    if (lane == 0) wait_or_abort(&empty_bar[st], ((n / p.nstage) - 1) & 1, &s_abort, p.status, 1u, k);
+            int tile = first;
+            for (int i = 0; i < cnt; ++i, tile += ncta) {
+                if (wrapped) {
+                    if (lane == 0) wait_parked_or_abort(&empty_bar[st], ph ^ 1u, &s_abort, p.status, 1u, k);
                     __syncwarp();
                 }
                 unsigned char* sbase = smem_raw + (size_t)st * p.slot_bytes;
@@ -265,6 +268,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         bulk_g2s(cb + op.woff_s, gs, bs, &full_bar[st], pol);
                     }
                 }
+                if (++st == p.nstage) { st = 0; ph ^= 1u; wrapped = true; }
             }
         }
         return;
@@ -273,15 +277,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     if (warp > kMegaConsumerWarps) {
         // ================= finalizers: fixed-order sum over k-warps + operator tail ========================
         const int fw = warp - kMegaConsumerWarps - 1;
-        int n = 0;
+        uint32_t n = 0;
         for (int k = 0; k < p.nops; ++k) {
             const MegaOp op = p.ops[k];
             if (op.ntiles == 0) continue;   // attention / argmax are published by the consumers
             const int first = my_first(op), cnt = my_count(op, first);
             for (int i = 0; i < cnt; ++i, ++n) {
-                if ((n % kMegaFinalWarps) != fw) continue;
+                if ((int)(n % kMegaFinalWarps) != fw) continue;
                 const int tile = first + i * ncta;
-                const int slot = n % kMegaRedSlots;
+                const int slot = (int)(n % kMegaRedSlots);
                 const float* red = &s_red[slot][0][0];
                 if (op.kind == MOP_SWIGLU || op.kind == MOP_QKV) {
                     const bool mine = lane < op.rwc;
@@ -291,7 +295,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     float2 cs = make_float2(1.f, 0.f);
                     if (op.kind == MOP_QKV && mine && r < ca.nrows && ca.m < 2)
                         cs = p.rope_table[(size_t)p.pos * (p.head_size >> 1) + (ca.row0 + r) % p.head_size];
-                    wait_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1, &s_abort, p.status, 3u, k);
+                    wait_parked_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1u, &s_abort, p.status, 3u, k);
                     if (mine && r < ca.nrows) {
                         float sa = 0.f, sb = 0.f;
                         for (int w = 0; w < op.kw; ++w) {
@@ -326,7 +330,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     if (lane < nrow) c = mega_chunk(op, p.head_size, tile, ch);
                     const bool mine = lane < nrow && r < c.nrows;
                     const int row = c.row0 + r;
-                    wait_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1, &s_abort, p.status, 3u, k);
+                    wait_parked_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1u, &s_abort, p.status, 3u, k);
                     if (mine) {
                         float sum = 0.f;
                         for (int w = 0; w < op.kw; ++w) sum += red[w * kMegaMaxRows + ch * op.rwc + r];
@@ -341,8 +345,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&free_bar[slot]);
             }
-            // this CTA's share of operator k is written: publish it (each finalizer warp fences its own stores)
-            __threadfence();
+            // this CTA's share of operator k is written: publish it. The warp barrier orders every lane's stores
+            // before lane 0's release, which is cumulative at device scope.
             __syncwarp();
             if (lane == 0) red_release_gpu_add(&p.done[k], 1u);
         }
@@ -350,17 +354,32 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     }
 
     // ================= consumers =========================================================================
-    int n_base = 0;  // running tile counter at the start of the current operator
+    uint32_t n_base = 0;  // running tile counter at the start of the current operator
+    int st_base = 0;      // ring stage of that tile, and the parity of its use count
+    uint32_t ph_base = 0;
+    long long t_dep = 0, t_full = 0, t_free = 0, t_attn = 0, t_pro = 0, t_all0 = clock64();
+    long long tk_dep[8] = {0,0,0,0,0,0,0,0}, tk_pro[8] = {0,0,0,0,0,0,0,0}, tk_run[8] = {0,0,0,0,0,0,0,0};
     for (int k = 0; k < p.nops; ++k) {
         const MegaOp op = p.ops[k];
 
         // ---- dependency: the previous operator's output is complete everywhere -----------------------------
-        if (k > 0) {
-            if (tid == 0) mega_wait_counter(&p.done[k - 1], expected * mega_arrivals(p.ops[k - 1]), &s_abort, p.status, 5u, k);
-            named_bar_sync(1, kConsThreads);
-        }
+        const int kk = (op.kind == MOP_RESID && op.rows > p.dim) ? 7 : op.kind;
+        long long tq0 = clock64();
+        // the previous operator's output is complete everywhere (acquire by one thread, then a CTA barrier)
+        auto wait_dependency = [&]() {
+            const long long td0 = clock64();
+            if (k > 0) {
+                if (tid == 0) mega_wait_counter(&p.done[k - 1], expected * mega_arrivals(p.ops[k - 1]), &s_abort, p.status, 5u, k);
+                named_bar_sync(1, kConsThreads);
+            }
+            const long long dt = clock64() - td0;
+            t_dep += dt;
+            tk_dep[kk] += dt;
+            tq0 += dt;   // keep the wait out of the prologue / attention accounting
+        };
 
         if (op.kind == MOP_ATTN) {
+            wait_dependency();
             // ---- attention of head `cta` (reference: mat_vec_strided / softmax / vec_mat kernels) -------------
             if (cta < p.heads_local) {
                 float* s_sc = reinterpret_cast<float*>(smem_raw + (size_t)p.nstage * p.slot_bytes);
@@ -422,10 +441,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 named_bar_sync(1, kConsThreads);
             }
             if (tid == 0) red_release_gpu_add(&p.done[k], 1u);
+            t_attn += clock64() - tq0;
             continue;
         }
 
         if (op.kind == MOP_ARGMAX) {
+            wait_dependency();
             // ---- greedy sample on CTA 0 (native/argmax_kernel.cu:8-46, lowest index on ties) --------------------
             if (cta == 0) {
                 float best = -INFINITY;
@@ -459,53 +480,87 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         const int u = kw_id * 32 + lane;
         const bool active = in_group && u < op.units;
         const bool is_int4 = op.fmt == 0;
-        const int nx = is_int4 ? 32 : 8;
+        const int nx = is_int4 ? 32 : 16;     // inputs per lane: one 16-byte weight vector (int4) or two (fp16)
         const int e0 = u * nx;
 
-        // input slice -> registers (xp: paired for the nibble masks when int4)
+        // Input vector, once per CTA: every consumer thread fetches 8 consecutive elements (the RMSNorm weights for
+        // them are fetched BEFORE the dependency wait, they are constants), the vector is normalised cooperatively
+        // (native/rmsnorm_kernel.cu:12-35) and staged in shared memory; each lane then takes its slice from there.
+        __half* s_vec = reinterpret_cast<__half*>(smem_raw + (size_t)p.nstage * p.slot_bytes);   // shares the attention scratch
+        const int nvec8 = op.rows >> 3;   // 16-byte pieces of the vector
+        uint4 gam[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (op.pro != 0) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+                if (tid + q * kConsThreads < nvec8) gam[q] = *reinterpret_cast<const uint4*>(op.gamma + (size_t)(tid + q * kConsThreads) * 8);
+        }
+        wait_dependency();
+
         uint32_t xp[16];
         float nlo = 0.f, nhi = 0.f, c1 = 0.f;
         {
             const __half* src = op.in;
             if (op.pro == 2) src = p.embed + (size_t)p.tokens[p.pos] * op.rows;   // native/embedding_kernel.cu:6-12
+            if (op.pro == 0) {
+                for (int i = tid; i < nvec8; i += kConsThreads)
+                    *reinterpret_cast<uint4*>(s_vec + (size_t)i * 8) = *reinterpret_cast<const uint4*>(src + (size_t)i * 8);
+            } else {
+                uint4 xv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                float ss = 0.f;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int i = tid + q * kConsThreads;
+                    if (i < nvec8) {
+                        xv[q] = *reinterpret_cast<const uint4*>(src + (size_t)i * 8);
+                        if (op.pro == 2 && cta == 0) *reinterpret_cast<uint4*>(p.x + (size_t)i * 8) = xv[q];  // residual stream := embedding row
+                        const uint32_t w4[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float a0 = half_bits_to_float(lo16(w4[e])), a1 = half_bits_to_float(hi16(w4[e]));
+                            ss = fmaf(a0, a0, ss);
+                            ss = fmaf(a1, a1, ss);
+                        }
+                    }
+                }
+                ss = warp_sum(ss);
+                float* part = &s_part[k & 1][0][0];
+                if (lane == 0) part[warp] = ss;
+                named_bar_sync(1, kConsThreads);
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kMegaConsumerWarps; ++w) tot += part[w];
+                const float rms = 1.0f / sqrtf(tot / (float)op.rows + p.eps);
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int i = tid + q * kConsThreads;
+                    if (i < nvec8) {
+                        const uint32_t w4[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
+                        const uint32_t g4[4] = {gam[q].x, gam[q].y, gam[q].z, gam[q].w};
+                        uint32_t o4[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = rms * half_bits_to_float(lo16(g4[e])) * half_bits_to_float(lo16(w4[e]));
+                            const float hi = rms * half_bits_to_float(hi16(g4[e])) * half_bits_to_float(hi16(w4[e]));
+                            o4[e] = (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(s_vec + (size_t)i * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+                    }
+                }
+            }
+            named_bar_sync(1, kConsThreads);
             uint32_t xr[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) xr[i] = 0u;
             if (active) {
-                if (is_int4) {
-                    mega_load_slice<32>(src, op.rows, e0, xr);
-                } else {
-                    uint32_t t4[4];
-                    mega_load_slice<8>(src, op.rows, e0, t4);
+                const uint4* sv = reinterpret_cast<const uint4*>(s_vec + e0);
+                const int nv = is_int4 ? 4 : 2;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) xr[i] = t4[i];
+                for (int v = 0; v < 4; ++v) {
+                    if (v < nv && e0 + v * 8 + 8 <= op.rows) {
+                        const uint4 t = sv[v];
+                        xr[4 * v] = t.x; xr[4 * v + 1] = t.y; xr[4 * v + 2] = t.z; xr[4 * v + 3] = t.w;
+                    }
                 }
-            }
-            if (op.pro == 2 && cta == 0 && group == 0 && active) {
-                // the residual stream starts as the embedding row: one CTA stores it for the later residual adds
-                uint4* dst = reinterpret_cast<uint4*>(p.x + e0);
-                if (is_int4) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) dst[v] = make_uint4(xr[4 * v], xr[4 * v + 1], xr[4 * v + 2], xr[4 * v + 3]);
-                } else {
-                    dst[0] = make_uint4(xr[0], xr[1], xr[2], xr[3]);
-                }
-            }
-            if (op.pro != 0) {
-                float ss = 0.f;
-                if (is_int4) ss = slice_sumsq<32>(xr);
-                else { uint32_t t4[4] = {xr[0], xr[1], xr[2], xr[3]}; ss = slice_sumsq<8>(t4); }
-                if (in_group && lane == 0) s_part[group][kw_id] = ss;
-                named_bar_sync(1, kConsThreads);
-                float tot = 0.f;
-                const int g = in_group ? group : 0;
-                for (int w = 0; w < op.kw; ++w) tot += s_part[g][w];
-                if (active) {
-                    if (is_int4) mega_norm_slice<32>(op.gamma, op.rows, e0, tot, p.eps, xr);
-                    else { uint32_t t4[4] = {xr[0], xr[1], xr[2], xr[3]}; mega_norm_slice<8>(op.gamma, op.rows, e0, tot, p.eps, t4);
-                           xr[0] = t4[0]; xr[1] = t4[1]; xr[2] = t4[2]; xr[3] = t4[3]; }
-                }
-                named_bar_sync(1, kConsThreads);   // s_part is reused by the next operator
             }
             if (is_int4) {
                 float se = 0.f, so = 0.f;
@@ -530,9 +585,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             }
         }
 
+        t_pro += clock64() - tq0;
+        tk_pro[kk] += clock64() - tq0;
+        const long long trun0 = clock64();
         const int g = u >> 2;
         const int zshift = (g & 7) * 4;
-        const uint32_t w_off = (uint32_t)(active ? u : 0) * 16u;
+        const uint32_t w_off = (uint32_t)(active ? u : 0) * (is_int4 ? 16u : 32u);
         const uint32_t z_off = op.woff_z + (uint32_t)(active ? (g >> 3) : 0) * 4u;
         const uint32_t s_off = op.woff_s + (uint32_t)(active ? g : 0) * 2u;
         const uint32_t w_row = (uint32_t)op.wsize * 4u, z_row = (uint32_t)op.zsize * 4u, s_row = (uint32_t)op.ssize * 2u;
@@ -540,14 +598,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         // arrival weights: the fixed barrier count is met by (kw - 1) single arrivals + one weighted arrival per tile
         const uint32_t my_arrive = (kw_id == 0) ? (kBarCount - (uint32_t)op.kw + 1u) : 1u;
 
-        for (int i = 0; i < cnt; ++i) {
-            const int n = n_base + i;
-            const int owner = i % op.groups;
-            if (!in_group || owner != group) continue;   // another group's tile (idle warps take none)
-            const int st = n % p.nstage;
-            wait_or_abort(&full_bar[st], (n / p.nstage) & 1, &s_abort, p.status, 2u, k);
-            const int slot = n % kMegaRedSlots;
-            bool slot_ready = n < kMegaRedSlots;
+        // tiles i = group, group + groups, ... belong to this group (idle warps take none)
+        int st = st_base + group;
+        uint32_t ph = ph_base;
+        while (st >= p.nstage) { st -= p.nstage; ph ^= 1u; }
+        for (int i = group; in_group && i < cnt; i += op.groups) {
+            const uint32_t n = n_base + (uint32_t)i;
+            long long tw0 = clock64();
+            wait_or_abort(&full_bar[st], ph, &s_abort, p.status, 2u, k);
+            t_full += clock64() - tw0;
+            const int slot = (int)(n % kMegaRedSlots);
+            bool slot_ready = n < (uint32_t)kMegaRedSlots;
             float resid[2] = {0.f, 0.f};
             if (op.kind == MOP_RESID && kw_id == 0 && (lane & 7) == 0 && (lane >> 3) < op.rwc) {
                 const int tile = first + i * ncta;
@@ -559,7 +620,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             for (int c = 0; c < op.nch; ++c) {
                 const uint32_t cb = ring + (uint32_t)st * p.slot_bytes + (uint32_t)c * op.chunk_bytes;
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
-                if (is_int4) {
+                if (p.debug & 1) {
+                } else if (is_int4) {
                     uint4 wv[4];
                     uint32_t zw[4];
                     unsigned short sc[4];
@@ -592,20 +654,31 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         if (r < op.rwc) {
-                            uint4 wv;
+                            uint4 wv, wu;
                             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                                          : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
                                          : "r"(cb + w_off + r * w_row));
-                            float a0 = 0.f, a1 = 0.f;
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(wu.x), "=r"(wu.y), "=r"(wu.z), "=r"(wu.w)
+                                         : "r"(cb + w_off + r * w_row + 16u));
+                            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
                             a0 = fma_f16_f32(lo16(wv.x), lo16(xp[0]), a0);
                             a1 = fma_f16_f32(hi16(wv.x), hi16(xp[0]), a1);
-                            a0 = fma_f16_f32(lo16(wv.y), lo16(xp[1]), a0);
-                            a1 = fma_f16_f32(hi16(wv.y), hi16(xp[1]), a1);
+                            a2 = fma_f16_f32(lo16(wv.y), lo16(xp[1]), a2);
+                            a3 = fma_f16_f32(hi16(wv.y), hi16(xp[1]), a3);
                             a0 = fma_f16_f32(lo16(wv.z), lo16(xp[2]), a0);
                             a1 = fma_f16_f32(hi16(wv.z), hi16(xp[2]), a1);
-                            a0 = fma_f16_f32(lo16(wv.w), lo16(xp[3]), a0);
-                            a1 = fma_f16_f32(hi16(wv.w), hi16(xp[3]), a1);
-                            v[r] = active ? (a0 + a1) : 0.f;
+                            a2 = fma_f16_f32(lo16(wv.w), lo16(xp[3]), a2);
+                            a3 = fma_f16_f32(hi16(wv.w), hi16(xp[3]), a3);
+                            a0 = fma_f16_f32(lo16(wu.x), lo16(xp[4]), a0);
+                            a1 = fma_f16_f32(hi16(wu.x), hi16(xp[4]), a1);
+                            a2 = fma_f16_f32(lo16(wu.y), lo16(xp[5]), a2);
+                            a3 = fma_f16_f32(hi16(wu.y), hi16(xp[5]), a3);
+                            a0 = fma_f16_f32(lo16(wu.z), lo16(xp[6]), a0);
+                            a1 = fma_f16_f32(hi16(wu.z), hi16(xp[6]), a1);
+                            a2 = fma_f16_f32(lo16(wu.w), lo16(xp[7]), a2);
+                            a3 = fma_f16_f32(hi16(wu.w), hi16(xp[7]), a3);
+                            v[r] = active ? ((a0 + a1) + (a2 + a3)) : 0.f;
                         }
                     }
                 }
@@ -616,7 +689,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 }
                 transpose_reduce<4>(v, lane);
                 if (!slot_ready) {
-                    wait_or_abort(&free_bar[slot], ((n / kMegaRedSlots) - 1) & 1, &s_abort, p.status, 4u, k);
+                    long long tf0 = clock64();
+                    wait_or_abort(&free_bar[slot], ((n / kMegaRedSlots) - 1u) & 1u, &s_abort, p.status, 4u, k);
+                    t_free += clock64() - tf0;
                     slot_ready = true;
                 }
                 if ((lane & 7) == 0 && (lane >> 3) < op.rwc) s_red[slot][kw_id][c * op.rwc + (lane >> 3)] = v[0];
@@ -625,8 +700,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_n(&done_bar[slot], my_arrive);
+            st += op.groups;
+            while (st >= p.nstage) { st -= p.nstage; ph ^= 1u; }
         }
-        n_base += cnt;
+        tk_run[kk] += clock64() - trun0;
+        n_base += (uint32_t)cnt;
+        st_base += cnt % p.nstage;   // one division per operator
+        ph_base ^= (uint32_t)(cnt / p.nstage) & 1u;
+        if (st_base >= p.nstage) { st_base -= p.nstage; ph_base ^= 1u; }
+    }
+    if (p.prof && tid == 0) {
+        long long* o = p.prof + (size_t)cta * 64;
+        o[0] = clock64() - t_all0; o[1] = t_dep; o[2] = t_full; o[3] = t_free; o[4] = t_attn; o[5] = t_pro;
+        for (int q = 0; q < 8; ++q) { o[8 + q] = tk_dep[q]; o[16 + q] = tk_pro[q]; o[24 + q] = tk_run[q]; }
     }
 }
 

@@ -177,6 +177,7 @@ struct Model {
     unsigned int* mega_done = nullptr;
     int mega_nops = 0, mega_nstage = 0, mega_slot = 0, mega_att_bytes = 0, mega_smem = 0, mega_grid = 0;
     unsigned int mega_seq = 0;
+    long long* mega_prof = nullptr;
 };
 
 #define ML2_CUDA(call)                                                                       \
@@ -402,13 +403,13 @@ static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols)
         if ((rows % 32) || (op.ssize & 1)) return false;   // 4-row runs of scales must be 16-byte multiples
         op.rwc = 4;
     } else {
-        if (rows % 8) return false;
+        if (rows % 16) return false;   // a lane owns two 16-byte vectors of every fp16 row
         op.wsize = rows / 2;
         op.zsize = op.ssize = 0;
         op.rwc = (rows * 2 * 4 <= 24 * 1024) ? 4 : 2;
     }
     if (cols % op.rwc) return false;
-    op.units = op.wsize / 4;
+    op.units = fmt == 0 ? op.wsize / 4 : op.wsize / 8;   // lane slots per row
     op.kw = ceil_div(op.units, 32);
     if (op.kw > kMegaConsumerWarps) return false;
     op.groups = std::min(kMegaMaxGroups, kMegaConsumerWarps / op.kw);
@@ -484,7 +485,9 @@ static int build_mega(Model* m)
     for (const MegaOp& op : ops)
         if (op.ntiles > 0) slot = std::max(slot, op.nch * op.chunk_bytes);
     slot = (slot + 127) & ~127;
-    const int att_bytes = ((c.seq_len * 4) + 127) & ~127;
+    const int widest = std::max(std::max(dim, m->hidden_local), m->dim_local);
+    if (dim > 2 * 8 * kMegaConsumerWarps * 32) return ML2_OK;   // a normalised input vector is fetched as two pieces per thread
+    const int att_bytes = (std::max(c.seq_len * 4, widest * 2) + 127) & ~127;
     const int budget = 200 * 1024;
     int nstage = (budget - att_bytes) / slot;
     if (nstage > kMegaMaxStages) nstage = kMegaMaxStages;
@@ -507,6 +510,10 @@ static int build_mega(Model* m)
     }
     ML2_CUDA(cudaMemsetAsync(m->mega_done, 0, ops.size() * sizeof(unsigned int), m->stream));
     ML2_CUDA(cudaStreamSynchronize(m->stream));
+    if (getenv("ML2_MEGA_PROF") && !m->mega_prof) {
+        ML2_CUDA(cudaMalloc(&m->mega_prof, (size_t)m->mega_grid * 64 * sizeof(long long)));
+        ML2_CUDA(cudaMemset(m->mega_prof, 0, (size_t)m->mega_grid * 64 * sizeof(long long)));
+    }
     m->mega_seq = 0;
     m->mega_ok = true;
     return ML2_OK;
@@ -530,6 +537,8 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     prm.kv_row_stride = m->dim_local; prm.vocab = m->cfg.vocab_size;
     prm.eps = m->eps; prm.scale = 1.0f / sqrtf((float)m->head_size);
     prm.nstage = m->mega_nstage; prm.slot_bytes = m->mega_slot; prm.att_cap = m->cfg.seq_len;
+    prm.prof = m->mega_prof;
+    { const char* d = getenv("ML2_MEGA_DEBUG"); prm.debug = d ? atoi(d) : 0; }
     void* args[] = {&prm};
     ML2_CUDA(cudaLaunchCooperativeKernel((const void*)decode_token_kernel, dim3(m->mega_grid), dim3(kMegaThreads), args,
                                          (size_t)m->mega_smem, m->stream));
@@ -849,6 +858,15 @@ int ml2_model_read_logits(ml2_model* h, void* logits_host_f16)
     if (!m || !logits_host_f16) return fail(ML2_E_INVALID, "read_logits: null argument");
     ML2_CUDA(cudaMemcpyAsync(logits_host_f16, m->logits, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, m->stream));
     ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
+int ml2_model_debug_prof(ml2_model* h, long long* out, int n)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !out || !m->mega_prof) return fail(ML2_E_STATE, "no profile buffer (set ML2_MEGA_PROF=1 before the first forward)");
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    ML2_CUDA(cudaMemcpy(out, m->mega_prof, (size_t)std::min(n, m->mega_grid * 64) * sizeof(long long), cudaMemcpyDeviceToHost));
     return ML2_OK;
 }
 

@@ -225,6 +225,22 @@ __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, vo
     }
 }
 
+// The same for roles off the critical path (producer, finalizers): the hardware parks the thread between polls,
+// so a waiting warp does not take issue slots from the arithmetic warps.
+__device__ __forceinline__ void wait_parked_or_abort(uint64_t* bar, uint32_t parity, volatile unsigned int* abort_flag,
+                                                     DeviceStatus* status, unsigned int code, int tile)
+{
+    for (uint32_t i = 0; i < (kSpinLimit >> 6); ++i) {
+        if (mbar_try_wait_suspend(bar, parity, 20000u)) return;
+        if ((i & 15u) == 15u && *abort_flag) return;
+    }
+    *abort_flag = 1;
+    if (status) {
+        atomicExch(&status->error, code);
+        status->detail = (unsigned int)tile;
+    }
+}
+
 template <Fmt F, Epi E, Pro P, int RW>
 __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecParams p)
 {
@@ -268,7 +284,7 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
             const int tile = blockIdx.x + i * gridDim.x;
             const int st = i % p.nstage;
             if (i >= p.nstage) {
-                if (lane == 0) wait_or_abort(&empty_bar[st], ((i / p.nstage) - 1) & 1, &s_abort, p.status, 1u, tile);
+                if (lane == 0) wait_parked_or_abort(&empty_bar[st], ((i / p.nstage) - 1) & 1, &s_abort, p.status, 1u, tile);
                 __syncwarp();
             }
             unsigned char* sbase = smem_raw + (size_t)st * stage_bytes;
@@ -350,7 +366,7 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
                 float2 cs = make_float2(1.f, 0.f);
                 if (E == Epi::QKVRope && mine && r < ca.nrows && ca.m < 2)
                     cs = p.rope_table[(size_t)pos * (p.head_size >> 1) + (ca.row0 + r) % p.head_size];
-                wait_or_abort(&done_bar[slot], (i / kRedSlots) & 1, &s_abort, p.status, 3u, tile);
+                wait_parked_or_abort(&done_bar[slot], (i / kRedSlots) & 1, &s_abort, p.status, 3u, tile);
                 if (mine && r < ca.nrows) {
                     float sa = 0.f, sb = 0.f;
                     for (int k = 0; k < p.kw; ++k) {
@@ -388,7 +404,7 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
                 const int row = c.row0 + r;
                 float resid = 0.f;
                 if (E == Epi::Residual && mine) resid = __half2float(p.out[0][row]);  // issued before the wait
-                wait_or_abort(&done_bar[slot], (i / kRedSlots) & 1, &s_abort, p.status, 3u, tile);
+                wait_parked_or_abort(&done_bar[slot], (i / kRedSlots) & 1, &s_abort, p.status, 3u, tile);
                 if (mine) {
                     float sum = 0.f;
                     for (int k = 0; k < p.kw; ++k) sum += red[k * kMaxR + lane];
