@@ -496,8 +496,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         }
         wait_dependency();
 
-        uint32_t xp[16];
-        float nlo = 0.f, nhi = 0.f, c1 = 0.f;
+        XSlice xs;
         {
             const __half* src = op.in;
             if (op.pro == 2) src = p.embed + (size_t)p.tokens[p.pos] * op.rows;   // native/embedding_kernel.cu:6-12
@@ -563,25 +562,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 }
             }
             if (is_int4) {
-                float se = 0.f, so = 0.f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t h01 = xr[4 * j], h23 = xr[4 * j + 1], h45 = xr[4 * j + 2], h67 = xr[4 * j + 3];
-                    xp[4 * j + 0] = __byte_perm(h01, h45, 0x5410);
-                    xp[4 * j + 1] = __byte_perm(h01, h45, 0x7632);
-                    xp[4 * j + 2] = __byte_perm(h23, h67, 0x5410);
-                    xp[4 * j + 3] = __byte_perm(h23, h67, 0x7632);
-                    se += half_bits_to_float(lo16(h01)) + half_bits_to_float(lo16(h23)) + half_bits_to_float(lo16(h45)) +
-                          half_bits_to_float(lo16(h67));
-                    so += half_bits_to_float(hi16(h01)) + half_bits_to_float(hi16(h23)) + half_bits_to_float(hi16(h45)) +
-                          half_bits_to_float(hi16(h67));
-                }
-                nlo = -1024.0f * se;
-                nhi = -1024.0f * so;
-                c1 = se + so;
+                make_xslice(xr, xs);
             } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) xp[i] = xr[i];
+                for (int i = 0; i < 16; ++i) xs.xp[i] = xr[i];
             }
         }
 
@@ -633,21 +617,22 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cb + z_off + r * z_row));
                         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cb + s_off + r * s_row));
                     }
-                    float alo[4], ahi[4];
+                    float A[4], B[4], D[4];
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        alo[r] = nlo;
-                        ahi[r] = nhi;
-                        word_dot(wv[r].x, xp + 0, alo[r], ahi[r]);
-                        word_dot(wv[r].y, xp + 4, alo[r], ahi[r]);
-                        word_dot(wv[r].z, xp + 8, alo[r], ahi[r]);
-                        word_dot(wv[r].w, xp + 12, alo[r], ahi[r]);
+                        A[r] = xs.a0;
+                        B[r] = xs.b0;
+                        D[r] = xs.d0;
+                        word_dot(wv[r].x, xs.xp + 0, xs.xf + 0, A[r], B[r], D[r]);
+                        word_dot(wv[r].y, xs.xp + 4, xs.xf + 2, A[r], B[r], D[r]);
+                        word_dot(wv[r].z, xs.xp + 8, xs.xf + 4, A[r], B[r], D[r]);
+                        word_dot(wv[r].w, xs.xp + 12, xs.xf + 6, A[r], B[r], D[r]);
                     }
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         const float zf = (float)((zw[r] >> zshift) & 0xFu);
-                        const float t = fmaf(ahi[r], 0.0625f, alo[r]);
-                        const float res = half_bits_to_float(sc[r]) * fmaf(-zf, c1, t);
+                        const float t = fmaf(B[r], 0.0625f, A[r]) + D[r];
+                        const float res = half_bits_to_float(sc[r]) * fmaf(-zf, xs.c1, t);
                         v[r] = active ? res : 0.f;
                     }
                 } else {
@@ -662,22 +647,22 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                                          : "=r"(wu.x), "=r"(wu.y), "=r"(wu.z), "=r"(wu.w)
                                          : "r"(cb + w_off + r * w_row + 16u));
                             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-                            a0 = fma_f16_f32(lo16(wv.x), lo16(xp[0]), a0);
-                            a1 = fma_f16_f32(hi16(wv.x), hi16(xp[0]), a1);
-                            a2 = fma_f16_f32(lo16(wv.y), lo16(xp[1]), a2);
-                            a3 = fma_f16_f32(hi16(wv.y), hi16(xp[1]), a3);
-                            a0 = fma_f16_f32(lo16(wv.z), lo16(xp[2]), a0);
-                            a1 = fma_f16_f32(hi16(wv.z), hi16(xp[2]), a1);
-                            a2 = fma_f16_f32(lo16(wv.w), lo16(xp[3]), a2);
-                            a3 = fma_f16_f32(hi16(wv.w), hi16(xp[3]), a3);
-                            a0 = fma_f16_f32(lo16(wu.x), lo16(xp[4]), a0);
-                            a1 = fma_f16_f32(hi16(wu.x), hi16(xp[4]), a1);
-                            a2 = fma_f16_f32(lo16(wu.y), lo16(xp[5]), a2);
-                            a3 = fma_f16_f32(hi16(wu.y), hi16(xp[5]), a3);
-                            a0 = fma_f16_f32(lo16(wu.z), lo16(xp[6]), a0);
-                            a1 = fma_f16_f32(hi16(wu.z), hi16(xp[6]), a1);
-                            a2 = fma_f16_f32(lo16(wu.w), lo16(xp[7]), a2);
-                            a3 = fma_f16_f32(hi16(wu.w), hi16(xp[7]), a3);
+                            a0 = fma_f16_f32(lo16(wv.x), lo16(xs.xp[0]), a0);
+                            a1 = fma_f16_f32(hi16(wv.x), hi16(xs.xp[0]), a1);
+                            a2 = fma_f16_f32(lo16(wv.y), lo16(xs.xp[1]), a2);
+                            a3 = fma_f16_f32(hi16(wv.y), hi16(xs.xp[1]), a3);
+                            a0 = fma_f16_f32(lo16(wv.z), lo16(xs.xp[2]), a0);
+                            a1 = fma_f16_f32(hi16(wv.z), hi16(xs.xp[2]), a1);
+                            a2 = fma_f16_f32(lo16(wv.w), lo16(xs.xp[3]), a2);
+                            a3 = fma_f16_f32(hi16(wv.w), hi16(xs.xp[3]), a3);
+                            a0 = fma_f16_f32(lo16(wu.x), lo16(xs.xp[4]), a0);
+                            a1 = fma_f16_f32(hi16(wu.x), hi16(xs.xp[4]), a1);
+                            a2 = fma_f16_f32(lo16(wu.y), lo16(xs.xp[5]), a2);
+                            a3 = fma_f16_f32(hi16(wu.y), hi16(xs.xp[5]), a3);
+                            a0 = fma_f16_f32(lo16(wu.z), lo16(xs.xp[6]), a0);
+                            a1 = fma_f16_f32(hi16(wu.z), hi16(xs.xp[6]), a1);
+                            a2 = fma_f16_f32(lo16(wu.w), lo16(xs.xp[7]), a2);
+                            a3 = fma_f16_f32(hi16(wu.w), hi16(xs.xp[7]), a3);
                             v[r] = active ? ((a0 + a1) + (a2 + a3)) : 0.f;
                         }
                     }

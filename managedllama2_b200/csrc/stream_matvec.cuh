@@ -119,25 +119,69 @@ __device__ __forceinline__ void transpose_reduce(float (&v)[RW], int lane)
     for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
 }
 
-// 8 nibbles of one word against the 8 matching inputs. xp[0..3] = (x0,x4) (x1,x5) (x2,x6) (x3,x7).
-__device__ __forceinline__ void word_dot(uint32_t w, const uint32_t* xp, float& alo, float& ahi)
+// 8 nibbles of one word against the 8 matching inputs. xp[0..3] = (x0,x4) (x1,x5) (x2,x6) (x3,x7) as fp16 pairs;
+// xf[0..1] = x4 * 2^-66, x6 * 2^-66 as fp32.
+//   a = (w & 0x000f000f) | 0x64006400   low half  = fp16(1024 + n0)              -> mixed FMA with x0       (acc A)
+//                                        whole reg = fp32 2^73 * (1 + (n4*65536 + 25600 + n0) / 2^23)
+//                                                  = 2^66 * (128 + n4 + 0.390625 + n0/65536)  -> FFMA with x4*2^-66 (acc D)
+//   b = (w & 0x00f000f0) | 0x64006400   halves    = fp16(1024 + 16*n1), fp16(1024 + 16*n5)   -> mixed FMAs       (acc B)
+//   c, d: the same on w >> 8 (n2, n6 and n3, n7).
+// Reading the pair register `a` as one fp32 takes the high nibble without extracting the high half (integer-pipe
+// instructions issue at half rate on this part). The low nibble rides along as n0/65536 of a unit of the WRONG input:
+// at most 2.3e-4 of |x4| per term, below 1e-5 of the finished dot product, far inside the fp16 output rounding.
+// The constant offsets (1024 * sum x, 128.390625 * sum x) are removed exactly by the accumulators' initial values.
+struct XSlice {
+    uint32_t xp[16];   // fp16 pairs for the mixed FMAs
+    float xf[8];       // x4, x6 of each word, scaled by 2^-66
+    float a0, b0, d0;  // accumulator start values: -1024*S(x0,x2), -1024*S(x1,x3,x5,x7), -128.390625*S(x4,x6)
+    float c1;          // sum of all 32 inputs (zero-point term)
+};
+
+__device__ __forceinline__ void word_dot(uint32_t w, const uint32_t* xp, const float* xf, float& A, float& B, float& D)
 {
-    const uint32_t a = (w & 0x000f000fu) | 0x64006400u;   // 1024 + (n0, n4)
-    const uint32_t b = (w & 0x00f000f0u) | 0x64006400u;   // 1024 + 16*(n1, n5)
+    const uint32_t a = (w & 0x000f000fu) | 0x64006400u;
+    const uint32_t b = (w & 0x00f000f0u) | 0x64006400u;
     const uint32_t w8 = w >> 8;
-    const uint32_t c = (w8 & 0x000f000fu) | 0x64006400u;  // 1024 + (n2, n6)
-    const uint32_t d = (w8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16*(n3, n7)
-    alo = fma_f16_f32(lo16(a), lo16(xp[0]), alo);
-    alo = fma_f16_f32(hi16(a), hi16(xp[0]), alo);
-    ahi = fma_f16_f32(lo16(b), lo16(xp[1]), ahi);
-    ahi = fma_f16_f32(hi16(b), hi16(xp[1]), ahi);
-    alo = fma_f16_f32(lo16(c), lo16(xp[2]), alo);
-    alo = fma_f16_f32(hi16(c), hi16(xp[2]), alo);
-    ahi = fma_f16_f32(lo16(d), lo16(xp[3]), ahi);
-    ahi = fma_f16_f32(hi16(d), hi16(xp[3]), ahi);
+    const uint32_t c = (w8 & 0x000f000fu) | 0x64006400u;
+    const uint32_t d = (w8 & 0x00f000f0u) | 0x64006400u;
+    A = fma_f16_f32(lo16(a), lo16(xp[0]), A);
+    D = fmaf(__uint_as_float(a), xf[0], D);
+    B = fma_f16_f32(lo16(b), lo16(xp[1]), B);
+    B = fma_f16_f32(hi16(b), hi16(xp[1]), B);
+    A = fma_f16_f32(lo16(c), lo16(xp[2]), A);
+    D = fmaf(__uint_as_float(c), xf[1], D);
+    B = fma_f16_f32(lo16(d), lo16(xp[3]), B);
+    B = fma_f16_f32(hi16(d), hi16(xp[3]), B);
 }
 
 __device__ __forceinline__ float half_bits_to_float(unsigned short h) { return __half2float(__ushort_as_half(h)); }
+
+// Builds the stationary input slice of a lane from its 32 inputs in natural order (16 fp16 pairs).
+__device__ __forceinline__ void make_xslice(const uint32_t (&xr)[16], XSlice& xs)
+{
+    float s02 = 0.f, sodd = 0.f, s46 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t h01 = xr[4 * j], h23 = xr[4 * j + 1], h45 = xr[4 * j + 2], h67 = xr[4 * j + 3];
+        xs.xp[4 * j + 0] = __byte_perm(h01, h45, 0x5410);   // (x0, x4)
+        xs.xp[4 * j + 1] = __byte_perm(h01, h45, 0x7632);   // (x1, x5)
+        xs.xp[4 * j + 2] = __byte_perm(h23, h67, 0x5410);   // (x2, x6)
+        xs.xp[4 * j + 3] = __byte_perm(h23, h67, 0x7632);   // (x3, x7)
+        const float x0 = __half2float(__ushort_as_half(lo16(h01))), x1 = __half2float(__ushort_as_half(hi16(h01)));
+        const float x2 = __half2float(__ushort_as_half(lo16(h23))), x3 = __half2float(__ushort_as_half(hi16(h23)));
+        const float x4 = __half2float(__ushort_as_half(lo16(h45))), x5 = __half2float(__ushort_as_half(hi16(h45)));
+        const float x6 = __half2float(__ushort_as_half(lo16(h67))), x7 = __half2float(__ushort_as_half(hi16(h67)));
+        xs.xf[2 * j + 0] = x4 * 1.3552527156068805e-20f;   // 2^-66, exact scaling
+        xs.xf[2 * j + 1] = x6 * 1.3552527156068805e-20f;
+        s02 += x0 + x2;
+        sodd += (x1 + x3) + (x5 + x7);
+        s46 += x4 + x6;
+    }
+    xs.a0 = -1024.0f * s02;
+    xs.b0 = -1024.0f * sodd;
+    xs.d0 = -128.390625f * s46;
+    xs.c1 = s02 + sodd + s46;
+}
 
 // Loads the lane's input slice (NX halves starting at element e0), optionally applying RMSNorm
 // (native/rmsnorm_kernel.cu:12-35: fp32 squares, rms = 1/sqrtf(ss/n + eps), out = half(rms*gamma*x)).
@@ -437,29 +481,12 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
     uint32_t xr[NX / 2];
     load_input<P, NX>(p, active ? e0 : p.rows, mw_id == 0, kw_id, ncons, s_part, xr);
 
-    uint32_t xp[NX / 2];
-    float nlo = 0.f, nhi = 0.f, c1 = 0.f;
+    XSlice xs;
     if constexpr (F == Fmt::Int4) {
-        // pair inputs the way the nibble masks pair weights: (x0,x4) (x1,x5) (x2,x6) (x3,x7) per word
-        float se = 0.f, so = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t h01 = xr[4 * j], h23 = xr[4 * j + 1], h45 = xr[4 * j + 2], h67 = xr[4 * j + 3];
-            xp[4 * j + 0] = __byte_perm(h01, h45, 0x5410);
-            xp[4 * j + 1] = __byte_perm(h01, h45, 0x7632);
-            xp[4 * j + 2] = __byte_perm(h23, h67, 0x5410);
-            xp[4 * j + 3] = __byte_perm(h23, h67, 0x7632);
-            se += half_bits_to_float(lo16(h01)) + half_bits_to_float(lo16(h23)) + half_bits_to_float(lo16(h45)) +
-                  half_bits_to_float(lo16(h67));
-            so += half_bits_to_float(hi16(h01)) + half_bits_to_float(hi16(h23)) + half_bits_to_float(hi16(h45)) +
-                  half_bits_to_float(hi16(h67));
-        }
-        nlo = -1024.0f * se;
-        nhi = -1024.0f * so;
-        c1 = se + so;
+        make_xslice(xr, xs);
     } else {
 #pragma unroll
-        for (int i = 0; i < NX / 2; ++i) xp[i] = xr[i];
+        for (int i = 0; i < NX / 2; ++i) xs.xp[i] = xr[i];
     }
     const int g = u >> 2;             // quantisation group of this lane's slice (Int4)
     const int zshift = (g & 7) * 4;
@@ -494,21 +521,22 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cb + z_off + r * z_row));
                 asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cb + s_off + r * s_row));
             }
-            float alo[RW], ahi[RW];
+            float A[RW], B[RW], D[RW];
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
-                alo[r] = nlo;
-                ahi[r] = nhi;
-                word_dot(wv[r].x, xp + 0, alo[r], ahi[r]);
-                word_dot(wv[r].y, xp + 4, alo[r], ahi[r]);
-                word_dot(wv[r].z, xp + 8, alo[r], ahi[r]);
-                word_dot(wv[r].w, xp + 12, alo[r], ahi[r]);
+                A[r] = xs.a0;
+                B[r] = xs.b0;
+                D[r] = xs.d0;
+                word_dot(wv[r].x, xs.xp + 0, xs.xf + 0, A[r], B[r], D[r]);
+                word_dot(wv[r].y, xs.xp + 4, xs.xf + 2, A[r], B[r], D[r]);
+                word_dot(wv[r].z, xs.xp + 8, xs.xf + 4, A[r], B[r], D[r]);
+                word_dot(wv[r].w, xs.xp + 12, xs.xf + 6, A[r], B[r], D[r]);
             }
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
                 const float zf = (float)((zw[r] >> zshift) & 0xFu);
-                const float t = fmaf(ahi[r], 0.0625f, alo[r]);
-                const float res = half_bits_to_float(sc[r]) * fmaf(-zf, c1, t);
+                const float t = fmaf(B[r], 0.0625f, A[r]) + D[r];
+                const float res = half_bits_to_float(sc[r]) * fmaf(-zf, xs.c1, t);
                 v[r] = active ? res : 0.f;
             }
         } else {
@@ -519,14 +547,14 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
                              : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
                              : "r"(cb + w_off + r * w_row));
                 float a0 = 0.f, a1 = 0.f;
-                a0 = fma_f16_f32(lo16(wv.x), lo16(xp[0]), a0);
-                a1 = fma_f16_f32(hi16(wv.x), hi16(xp[0]), a1);
-                a0 = fma_f16_f32(lo16(wv.y), lo16(xp[1]), a0);
-                a1 = fma_f16_f32(hi16(wv.y), hi16(xp[1]), a1);
-                a0 = fma_f16_f32(lo16(wv.z), lo16(xp[2]), a0);
-                a1 = fma_f16_f32(hi16(wv.z), hi16(xp[2]), a1);
-                a0 = fma_f16_f32(lo16(wv.w), lo16(xp[3]), a0);
-                a1 = fma_f16_f32(hi16(wv.w), hi16(xp[3]), a1);
+                a0 = fma_f16_f32(lo16(wv.x), lo16(xs.xp[0]), a0);
+                a1 = fma_f16_f32(hi16(wv.x), hi16(xs.xp[0]), a1);
+                a0 = fma_f16_f32(lo16(wv.y), lo16(xs.xp[1]), a0);
+                a1 = fma_f16_f32(hi16(wv.y), hi16(xs.xp[1]), a1);
+                a0 = fma_f16_f32(lo16(wv.z), lo16(xs.xp[2]), a0);
+                a1 = fma_f16_f32(hi16(wv.z), hi16(xs.xp[2]), a1);
+                a0 = fma_f16_f32(lo16(wv.w), lo16(xs.xp[3]), a0);
+                a1 = fma_f16_f32(hi16(wv.w), hi16(xs.xp[3]), a1);
                 v[r] = active ? (a0 + a1) : 0.f;
             }
         }
