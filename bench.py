@@ -354,7 +354,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             dom_bytes = nbytes[dom]
             achieved = nbytes[dom] / avg_us[dom] * 1e-3
         threads = os.cpu_count() or 1
-        if world == 1:
+        if world == 1 and not args.no_cpu:
             cpu_val, t_layer, t_cls = cpu_tokens_per_s(cfg, threads, 3)
             cpu_baseline = {"value": cpu_val, "unit": "tokens/s", "cores": threads, "kind": "port",
                             "sample": "3 repetitions of one layer's 7 int4 mat-vecs (C# reference arithmetic) x %d layers + "
@@ -365,8 +365,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             "metric": "decode tokens/s batch-1", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "llama2-%s-shape AWQ int4 g128, batch-1 greedy decode, %d-token prompt then decode" %
-                                   (args.config, PROMPT_LEN),
+            "config": {"workload": "llama2-%s-shape%s AWQ int4 g128, batch-1 greedy decode, %d-token prompt then decode" %
+                                   (args.config, (" cut to %d layers" % args.layers) if args.layers else "", PROMPT_LEN),
                        "parallelism": "tp%d" % world, "l2": "per-token working set %.2f GB per GPU, far larger than L2" % (tb / 1e9),
                        "bytes_per_token_per_gpu": tb},
             "hbm_frac_of_token": {"achieved_GB/s": tb * tokens_per_s / 1e9, "of_%s_peak" % peak_kind: tb * tokens_per_s / 1e9 / peak,
@@ -396,13 +396,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="13b", choices=sorted(CONFIGS))
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the shape with fewer layers (smaller device footprint)")
+    ap.add_argument("--no-cpu", action="store_true", help="profiling aid: skip the CPU baseline leg")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.layers > 0:
+        cfg["numLayers"] = args.layers
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank, world)
         return

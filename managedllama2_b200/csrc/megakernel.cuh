@@ -181,8 +181,11 @@ __device__ __forceinline__ float slice_sumsq(const uint32_t (&xr)[NX / 2])
     return warp_sum(ss);
 }
 
+// kProf adds cycle counters around the waits (diagnostics); the production instantiation carries none.
+template <bool kProf>
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const MegaParams p)
 {
+    auto now = [&]() -> long long { return kProf ? clock64() : 0ll; };
     extern __shared__ __align__(128) unsigned char smem_raw[];   // [ring: nstage * slot_bytes][attention scores: att_cap floats]
     __shared__ __align__(8) uint64_t full_bar[kMegaMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMegaMaxStages];
@@ -258,9 +261,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 uint32_t tx = live ? (bw + bz + bs) : 0u;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
-                if (lane == 0) mbar_arrive_expect_tx(&full_bar[st], tx);
+                const bool nocopy = (p.debug & 8) != 0;
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[st], nocopy ? 0u : tx);
                 __syncwarp();
-                if (live) {
+                if (live && !nocopy) {
                     unsigned char* cb = sbase + (size_t)lane * op.chunk_bytes;
                     bulk_g2s(cb, gw, bw, &full_bar[st], pol);
                     if (op.fmt == 0) {
@@ -287,7 +291,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 const int tile = first + i * ncta;
                 const int slot = (int)(n % kMegaRedSlots);
                 const float* red = &s_red[slot][0][0];
-                if (op.kind == MOP_SWIGLU || op.kind == MOP_QKV) {
+                if (p.debug & 4) {
+                    wait_parked_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1u, &s_abort, p.status, 3u, k);
+                } else if (op.kind == MOP_SWIGLU || op.kind == MOP_QKV) {
                     const bool mine = lane < op.rwc;
                     MegaChunk ca{0, 0, 0}, cb{0, 0, 0};
                     if (mine) { ca = mega_chunk(op, p.head_size, tile, 0); cb = mega_chunk(op, p.head_size, tile, 1); }
@@ -357,22 +363,22 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     uint32_t n_base = 0;  // running tile counter at the start of the current operator
     int st_base = 0;      // ring stage of that tile, and the parity of its use count
     uint32_t ph_base = 0;
-    long long t_dep = 0, t_full = 0, t_free = 0, t_attn = 0, t_pro = 0, t_all0 = clock64();
+    long long t_dep = 0, t_full = 0, t_free = 0, t_attn = 0, t_pro = 0, t_all0 = now();
     long long tk_dep[8] = {0,0,0,0,0,0,0,0}, tk_pro[8] = {0,0,0,0,0,0,0,0}, tk_run[8] = {0,0,0,0,0,0,0,0};
     for (int k = 0; k < p.nops; ++k) {
         const MegaOp op = p.ops[k];
 
         // ---- dependency: the previous operator's output is complete everywhere -----------------------------
         const int kk = (op.kind == MOP_RESID && op.rows > p.dim) ? 7 : op.kind;
-        long long tq0 = clock64();
+        long long tq0 = now();
         // the previous operator's output is complete everywhere (acquire by one thread, then a CTA barrier)
         auto wait_dependency = [&]() {
-            const long long td0 = clock64();
+            const long long td0 = now();
             if (k > 0) {
                 if (tid == 0) mega_wait_counter(&p.done[k - 1], expected * mega_arrivals(p.ops[k - 1]), &s_abort, p.status, 5u, k);
                 named_bar_sync(1, kConsThreads);
             }
-            const long long dt = clock64() - td0;
+            const long long dt = now() - td0;
             t_dep += dt;
             tk_dep[kk] += dt;
             tq0 += dt;   // keep the wait out of the prologue / attention accounting
@@ -441,7 +447,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 named_bar_sync(1, kConsThreads);
             }
             if (tid == 0) red_release_gpu_add(&p.done[k], 1u);
-            t_attn += clock64() - tq0;
+            t_attn += now() - tq0;
             continue;
         }
 
@@ -569,9 +575,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             }
         }
 
-        t_pro += clock64() - tq0;
-        tk_pro[kk] += clock64() - tq0;
-        const long long trun0 = clock64();
+        t_pro += now() - tq0;
+        tk_pro[kk] += now() - tq0;
+        const long long trun0 = now();
         const int g = u >> 2;
         const int zshift = (g & 7) * 4;
         const uint32_t w_off = (uint32_t)(active ? u : 0) * (is_int4 ? 16u : 32u);
@@ -588,9 +594,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         while (st >= p.nstage) { st -= p.nstage; ph ^= 1u; }
         for (int i = group; in_group && i < cnt; i += op.groups) {
             const uint32_t n = n_base + (uint32_t)i;
-            long long tw0 = clock64();
+            long long tw0 = now();
             wait_or_abort(&full_bar[st], ph, &s_abort, p.status, 2u, k);
-            t_full += clock64() - tw0;
+            t_full += now() - tw0;
             const int slot = (int)(n % kMegaRedSlots);
             bool slot_ready = n < (uint32_t)kMegaRedSlots;
             float resid[2] = {0.f, 0.f};
@@ -672,11 +678,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     __syncwarp();
                     if (lane == 0) mbar_arrive_n(&empty_bar[st], my_arrive);
                 }
-                transpose_reduce<4>(v, lane);
+                if (!(p.debug & 2)) transpose_reduce<4>(v, lane);
                 if (!slot_ready) {
-                    long long tf0 = clock64();
+                    long long tf0 = now();
                     wait_or_abort(&free_bar[slot], ((n / kMegaRedSlots) - 1u) & 1u, &s_abort, p.status, 4u, k);
-                    t_free += clock64() - tf0;
+                    t_free += now() - tf0;
                     slot_ready = true;
                 }
                 if ((lane & 7) == 0 && (lane >> 3) < op.rwc) s_red[slot][kw_id][c * op.rwc + (lane >> 3)] = v[0];
@@ -688,15 +694,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             st += op.groups;
             while (st >= p.nstage) { st -= p.nstage; ph ^= 1u; }
         }
-        tk_run[kk] += clock64() - trun0;
+        tk_run[kk] += now() - trun0;
         n_base += (uint32_t)cnt;
         st_base += cnt % p.nstage;   // one division per operator
         ph_base ^= (uint32_t)(cnt / p.nstage) & 1u;
         if (st_base >= p.nstage) { st_base -= p.nstage; ph_base ^= 1u; }
     }
-    if (p.prof && tid == 0) {
+    if (kProf && p.prof && tid == 0) {
         long long* o = p.prof + (size_t)cta * 64;
-        o[0] = clock64() - t_all0; o[1] = t_dep; o[2] = t_full; o[3] = t_free; o[4] = t_attn; o[5] = t_pro;
+        o[0] = now() - t_all0; o[1] = t_dep; o[2] = t_full; o[3] = t_free; o[4] = t_attn; o[5] = t_pro;
         for (int q = 0; q < 8; ++q) { o[8 + q] = tk_dep[q]; o[16 + q] = tk_pro[q]; o[24 + q] = tk_run[q]; }
     }
 }

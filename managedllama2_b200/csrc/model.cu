@@ -498,9 +498,10 @@ static int build_mega(Model* m)
     m->mega_smem = nstage * slot + att_bytes;
     m->mega_nops = (int)ops.size();
     m->mega_grid = m->ctx->sm_count;
-    ML2_CUDA(cudaFuncSetAttribute(decode_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, m->mega_smem));
+    ML2_CUDA(cudaFuncSetAttribute(decode_token_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->mega_smem));
+    ML2_CUDA(cudaFuncSetAttribute(decode_token_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->mega_smem));
     int per_sm = 0;
-    ML2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_token_kernel, kMegaThreads, m->mega_smem));
+    ML2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_token_kernel<false>, kMegaThreads, m->mega_smem));
     if (per_sm < 1) return ML2_OK;
     if (m->mega_ops) { cudaFree(m->mega_ops); m->mega_ops = nullptr; }
     ML2_CUDA(cudaMalloc(&m->mega_ops, ops.size() * sizeof(MegaOp)));
@@ -540,8 +541,8 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     prm.prof = m->mega_prof;
     { const char* d = getenv("ML2_MEGA_DEBUG"); prm.debug = d ? atoi(d) : 0; }
     void* args[] = {&prm};
-    ML2_CUDA(cudaLaunchCooperativeKernel((const void*)decode_token_kernel, dim3(m->mega_grid), dim3(kMegaThreads), args,
-                                         (size_t)m->mega_smem, m->stream));
+    const void* fn = m->mega_prof ? (const void*)decode_token_kernel<true> : (const void*)decode_token_kernel<false>;
+    ML2_CUDA(cudaLaunchCooperativeKernel(fn, dim3(m->mega_grid), dim3(kMegaThreads), args, (size_t)m->mega_smem, m->stream));
     ++m->ctx->launches;
     m->launches_per_token = 1;
     return ML2_OK;
