@@ -220,6 +220,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     ctx = ml2.CudaContext(local_rank)
     weights = ml2.synthetic_weights(ctx, config, seed=SEED, tp_size=world, tp_rank=rank)
     tr = ml2.Transformer(config, weights, ctx, tp_size=world, tp_rank=rank, nccl_id=nccl_id)
+    if dist is not None and os.environ.get("ML2_TP_FUSED", "1") == "1":
+        tr.attach_peers_with(dist)   # persistent kernel per GPU, all-reduce fused over peer memory
     sp = ctypes.c_void_p()
     _lib.check(tr.lib.ml2_model_stream(tr.handle, ctypes.byref(sp)))
     stream = torch.cuda.ExternalStream(sp.value)

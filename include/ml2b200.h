@@ -201,6 +201,16 @@ int ml2_model_set_tokens(ml2_model* model, const int* tokens_host, int first, in
 int ml2_model_put_token_async(ml2_model* model, int pos, const int* token_pinned_host);
 int ml2_model_read_token(ml2_model* model, int pos, int* token_host);
 int ml2_model_read_logits(ml2_model* model, void* logits_host_f16);
+/* Tensor-parallel persistent kernel (one launch per token per GPU, all-reduce fused into the operator hand-off):
+ * every rank owns one peer-visible buffer (counters, fp32 receive zones, logits). `ml2_model_comm_handle` writes
+ * its 64-byte CUDA IPC handle; the host exchanges the handles of all ranks (any transport) and passes them, in
+ * rank order, to `ml2_model_comm_attach`. Row-sharded mat-vecs then store their fp32 partials straight into every
+ * rank's receive zone (plain peer stores over NVLink, no multicast), publish with a system-scope release on every
+ * rank's counter, and the next operator adds the tp partials in rank order before the single fp16 rounding.
+ * Without attached peers the tensor-parallel model runs the CUDA-graph + ncclAllReduce path. All ranks must call
+ * ml2_model_forward the same number of times. */
+int ml2_model_comm_handle(ml2_model* model, void* out64);
+int ml2_model_comm_attach(ml2_model* model, const void* handles_rank_order, int n_ranks);
 /* Diagnostics: per-CTA cycle counters of the last persistent-kernel launch (16 values per CTA: total, dependency
  * waits, ring waits, partial-slot waits, attention, prologue); needs ML2_MEGA_PROF=1 in the environment. */
 int ml2_model_debug_prof(ml2_model* model, long long* out, int n);

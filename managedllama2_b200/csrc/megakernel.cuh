@@ -28,23 +28,33 @@ enum MegaOpKind : int { MOP_QKV = 0, MOP_ATTN = 1, MOP_RESID = 2, MOP_SWIGLU = 3
 struct MegaOp {
     int kind;
     int fmt;                 // 0 int4, 1 fp16 weights
-    int pro;                 // 0 plain input, 1 RMSNorm(in, gamma), 2 RMSNorm(embedding row of the token, gamma)
+    int pro;                 // 0 plain input, 1 RMSNorm(in, gamma), 2 RMSNorm(embedding row of the token, gamma),
+                             // 3 RMSNorm(in + sum over ranks of recv, gamma): residual add of a row-sharded mat-vec
     int rows, cols, nmat;    // d_in, d_out per matrix, matrices
     int wsize, zsize, ssize; // per-output sizes (words, words, halves)
     int units;               // 16-byte vectors per row
     int kw, groups;          // warps per group, groups per CTA
-    int nch, rwc;            // chunks per tile, rows per chunk
+    int nch, rwc;            // arithmetic chunks per tile, rows per chunk
+    int nruns, run_rows;     // copy sets ("runs" of consecutive rows) per tile, rows per run: nruns * run_rows = nch * rwc
     int ntiles;
-    int chunk_bytes, woff_z, woff_s;
+    int chunk_bytes, woff_z, woff_s;   // shared-memory bytes of one run and the offsets of its zeros / scales parts
     int rot;                 // rotation of the tile -> CTA assignment
+    int tp;                  // ranks summed into the input (pro 3) / receiving the output (MOP_PARTIAL, sharded MOP_CLS)
+    int out_row0;            // sharded classifier: first vocabulary row of this rank
     int pad;
     QWPtrs mat[3];
     __half* out[3];
     float* out_f32;
-    const __half* in;
+    const __half* in;        // pro 3: the residual stream BEFORE the all-reduced update
     const __half* gamma;
     const __half* kcache;    // attention: this layer's caches
     const __half* vcache;
+    // tensor parallel, fused all-reduce over peer memory (plain peer stores, no multicast):
+    const float* recv;       // pro 3: [tp][rows] fp32 partials that every rank (this one included) stored here
+    __half* x_next;          // pro 3: where CTA 0 stores the updated residual stream
+    float* peer_out[8];      // MOP_PARTIAL: this rank's row block inside every rank's receive zone
+    __half* peer_logits[8];  // sharded MOP_CLS: every rank's full logits buffer
+    unsigned int* peer_done[8];  // this operator's counter on every rank
 };
 
 struct MegaParams {
@@ -96,7 +106,12 @@ struct MegaChunk {
 };
 
 // arrivals one CTA makes on an operator's counter: every finalizer warp for weight operators, one thread otherwise
-__host__ __device__ __forceinline__ unsigned int mega_arrivals(const MegaOp& op) { return op.ntiles > 0 ? (unsigned int)kMegaFinalWarps : 1u; }
+__host__ __device__ __forceinline__ unsigned int mega_arrivals(const MegaOp& op)
+{
+    const unsigned int per_rank = op.ntiles > 0 ? (unsigned int)kMegaFinalWarps : 1u;
+    const bool shared = (op.kind == MOP_PARTIAL || op.kind == MOP_CLS) && op.tp > 1;   // every rank publishes on every rank
+    return shared ? per_rank * (unsigned int)op.tp : per_rank;
+}
 
 __device__ __forceinline__ MegaChunk mega_chunk(const MegaOp& op, int head_size, int tile, int c)
 {
@@ -122,12 +137,37 @@ __device__ __forceinline__ MegaChunk mega_chunk(const MegaOp& op, int head_size,
     return k;
 }
 
+// Copy set `run` of a tile: the consecutive rows one group of bulk copies brings in.
+__device__ __forceinline__ MegaChunk mega_run(const MegaOp& op, int head_size, int tile, int run)
+{
+    if (op.kind == MOP_SWIGLU || op.kind == MOP_QKV) return mega_chunk(op, head_size, tile, run);
+    MegaChunk k;
+    k.m = 0;
+    k.row0 = tile * op.run_rows;
+    int n = op.cols - k.row0;
+    n = n < 0 ? 0 : (n > op.run_rows ? op.run_rows : n);
+    k.nrows = run == 0 ? n : 0;
+    return k;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v)
+{
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // Device-wide dependency: waits until `counter` has collected `expected` arrivals (bounded).
 __device__ __forceinline__ void mega_wait_counter(const unsigned int* counter, unsigned int expected, volatile unsigned int* abort_flag,
-                                                  DeviceStatus* status, unsigned int code, int op_index)
+                                                  DeviceStatus* status, unsigned int code, int op_index, bool sys_scope)
 {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if ((int)(ld_acquire_gpu(counter) - expected) >= 0) return;
+        const unsigned int seen = sys_scope ? ld_acquire_sys(counter) : ld_acquire_gpu(counter);
+        if ((int)(seen - expected) >= 0) return;
         if ((i & 255u) == 255u && (*abort_flag || ld_acquire_gpu(&status->error))) { *abort_flag = 1; return; }
     }
     *abort_flag = 1;
@@ -244,7 +284,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 }
                 unsigned char* sbase = smem_raw + (size_t)st * p.slot_bytes;
                 MegaChunk c{0, 0, 0};
-                if (lane < op.nch) c = mega_chunk(op, p.head_size, tile, lane);
+                if (lane < op.nruns) c = mega_run(op, p.head_size, tile, lane);
                 const QWPtrs q = op.mat[c.m < op.nmat ? c.m : 0];
                 const uint32_t* gw = q.w + (size_t)c.row0 * op.wsize;
                 const uint32_t bw = (uint32_t)c.nrows * op.wsize * 4u;
@@ -344,8 +384,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         // travels in the extra k-row of the partial slot
                         if (op.kind == MOP_RESID)
                             op.out[0][row] = __float2half_rn(sum + red[op.kw * kMegaMaxRows + ch * op.rwc + r]);  // native/mat_vec_kernel.cu:154-156
-                        else if (op.kind == MOP_PARTIAL) op.out_f32[row] = sum;
-                        else op.out[0][row] = __float2half_rn(sum);
+                        else if (op.kind == MOP_PARTIAL) {
+                            // row-sharded mat-vec: this rank's fp32 partial goes straight into every rank's receive
+                            // zone (plain peer stores over NVLink); the residual add and the single fp16 rounding
+                            // happen where the sum is consumed
+                            for (int q = 0; q < op.tp; ++q) op.peer_out[q][row] = sum;
+                        } else if (op.tp > 1) {
+                            // vocabulary-sharded classifier: every rank ends up with the full logits
+                            const __half hv = __float2half_rn(sum);
+                            for (int q = 0; q < op.tp; ++q) op.peer_logits[q][op.out_row0 + row] = hv;
+                        } else {
+                            op.out[0][row] = __float2half_rn(sum);
+                        }
                     }
                 }
                 __syncwarp();
@@ -354,7 +404,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             // this CTA's share of operator k is written: publish it. The warp barrier orders every lane's stores
             // before lane 0's release, which is cumulative at device scope.
             __syncwarp();
-            if (lane == 0) red_release_gpu_add(&p.done[k], 1u);
+            if ((op.kind == MOP_PARTIAL || op.kind == MOP_CLS) && op.tp > 1) {
+                // published on every rank's counter: system-scope release after the peer stores of this warp
+                if (lane < op.tp) red_release_sys_add(op.peer_done[lane], 1u);
+            } else if (lane == 0) {
+                red_release_gpu_add(&p.done[k], 1u);
+            }
         }
         return;
     }
@@ -375,7 +430,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         auto wait_dependency = [&]() {
             const long long td0 = now();
             if (k > 0) {
-                if (tid == 0) mega_wait_counter(&p.done[k - 1], expected * mega_arrivals(p.ops[k - 1]), &s_abort, p.status, 5u, k);
+                if (tid == 0) {
+                    const MegaOp& prev = p.ops[k - 1];
+                    const bool sys = (prev.kind == MOP_PARTIAL || prev.kind == MOP_CLS) && prev.tp > 1;
+                    mega_wait_counter(&p.done[k - 1], expected * mega_arrivals(prev), &s_abort, p.status, 5u, k, sys);
+                }
                 named_bar_sync(1, kConsThreads);
             }
             const long long dt = now() - td0;
@@ -518,6 +577,27 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     if (i < nvec8) {
                         xv[q] = *reinterpret_cast<const uint4*>(src + (size_t)i * 8);
                         if (op.pro == 2 && cta == 0) *reinterpret_cast<uint4*>(p.x + (size_t)i * 8) = xv[q];  // residual stream := embedding row
+                        if (op.pro == 3) {
+                            // residual add of a row-sharded mat-vec: x := half(float(x) + sum over ranks of their fp32
+                            // partials), ranks in fixed order so that every rank rounds the same value
+                            // (rounding point of native/mat_vec_kernel.cu:154-156)
+                            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                            for (int r = 0; r < op.tp; ++r) {
+                                const float4* pr = reinterpret_cast<const float4*>(op.recv + (size_t)r * op.rows + (size_t)i * 8);
+                                const float4 p0 = pr[0], p1 = pr[1];
+                                acc[0] += p0.x; acc[1] += p0.y; acc[2] += p0.z; acc[3] += p0.w;
+                                acc[4] += p1.x; acc[5] += p1.y; acc[6] += p1.z; acc[7] += p1.w;
+                            }
+                            uint32_t w4r[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float lo = half_bits_to_float(lo16(w4r[e])) + acc[2 * e];
+                                const float hi = half_bits_to_float(hi16(w4r[e])) + acc[2 * e + 1];
+                                w4r[e] = (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+                            }
+                            xv[q] = make_uint4(w4r[0], w4r[1], w4r[2], w4r[3]);
+                            if (cta == 0) *reinterpret_cast<uint4*>(op.x_next + (size_t)i * 8) = xv[q];
+                        }
                         const uint32_t w4[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
@@ -608,7 +688,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 }
             }
             for (int c = 0; c < op.nch; ++c) {
-                const uint32_t cb = ring + (uint32_t)st * p.slot_bytes + (uint32_t)c * op.chunk_bytes;
+                // chunk c = rows [c*rwc, c*rwc + rwc) of the tile; they sit in run (c*rwc / run_rows) at row rin0 of that run
+                const int trow = c * op.rwc;
+                const int run = (op.run_rows == 8) ? (trow >> 3) : (op.run_rows == 4 ? (trow >> 2) : (trow >> 1));
+                const int rin0 = trow - run * op.run_rows;
+                const uint32_t cbase = ring + (uint32_t)st * p.slot_bytes + (uint32_t)run * op.chunk_bytes;
+                const uint32_t cb = cbase;   // weights of the run start here
+                const uint32_t cw = cbase + (uint32_t)rin0 * w_row;
+                const uint32_t cz = cbase + (uint32_t)rin0 * z_row;
+                const uint32_t cs = cbase + (uint32_t)rin0 * s_row;
+                (void)cb;
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
                 if (p.debug & 1) {
                 } else if (is_int4) {
@@ -619,9 +708,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     for (int r = 0; r < 4; ++r) {
                         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                                      : "=r"(wv[r].x), "=r"(wv[r].y), "=r"(wv[r].z), "=r"(wv[r].w)
-                                     : "r"(cb + w_off + r * w_row));
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cb + z_off + r * z_row));
-                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cb + s_off + r * s_row));
+                                     : "r"(cw + w_off + r * w_row));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cz + z_off + r * z_row));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cs + s_off + r * s_row));
                     }
                     float A[4], B[4], D[4];
 #pragma unroll
@@ -648,10 +737,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                             uint4 wv, wu;
                             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                                          : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
-                                         : "r"(cb + w_off + r * w_row));
+                                         : "r"(cw + w_off + r * w_row));
                             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                                          : "=r"(wu.x), "=r"(wu.y), "=r"(wu.z), "=r"(wu.w)
-                                         : "r"(cb + w_off + r * w_row + 16u));
+                                         : "r"(cw + w_off + r * w_row + 16u));
                             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
                             a0 = fma_f16_f32(lo16(wv.x), lo16(xs.xp[0]), a0);
                             a1 = fma_f16_f32(hi16(wv.x), hi16(xs.xp[0]), a1);

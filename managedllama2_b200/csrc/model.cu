@@ -178,6 +178,12 @@ struct Model {
     int mega_nops = 0, mega_nstage = 0, mega_slot = 0, mega_att_bytes = 0, mega_smem = 0, mega_grid = 0;
     unsigned int mega_seq = 0;
     long long* mega_prof = nullptr;
+    unsigned int* mega_done_ptr = nullptr;
+    __half* logits_view = nullptr;          // where the full logits of the persistent kernel land
+    // tensor parallel persistent kernel: one peer-visible buffer per rank (counters, receive zones, logits)
+    void* comm_local = nullptr;
+    void* comm_peer[8] = {};
+    bool comm_attached = false;
 };
 
 #define ML2_CUDA(call)                                                                       \
@@ -391,43 +397,77 @@ static double qweight_bytes(int rows, int cols)
 }
 
 // ---- persistent per-token kernel: operator list and launch ------------------------------------------------------
-static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols)
+static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, bool paired)
 {
     op.fmt = fmt;
     op.rows = rows;
     op.cols = cols;
+    op.tp = 1;
     if (fmt == 0) {
         op.ssize = ceil_div(rows, kGroup);
         op.wsize = ceil_div(rows, 32) * 4;
         op.zsize = ceil_div(op.ssize, 8);
-        if ((rows % 32) || (op.ssize & 1)) return false;   // 4-row runs of scales must be 16-byte multiples
+        if (rows % 32) return false;
         op.rwc = 4;
+        // a 4-row run of scales is 8*ssize bytes: with an odd group count only 8-row runs keep every bulk copy
+        // 16-byte aligned (paired tiles cannot use them: their two runs belong to different matrices / row blocks)
+        const bool odd = (op.ssize & 1) != 0;
+        if (odd && paired) return false;
+        op.run_rows = odd ? 8 : 4;
+        op.nruns = paired ? 2 : 1;
+        op.nch = paired ? 2 : op.run_rows / 4;
     } else {
         if (rows % 16) return false;   // a lane owns two 16-byte vectors of every fp16 row
         op.wsize = rows / 2;
         op.zsize = op.ssize = 0;
         op.rwc = (rows * 2 * 4 <= 24 * 1024) ? 4 : 2;
+        op.run_rows = op.rwc;
+        op.nruns = 1;
+        op.nch = 1;
     }
-    if (cols % op.rwc) return false;
+    if (cols % op.run_rows) return false;
     op.units = fmt == 0 ? op.wsize / 4 : op.wsize / 8;   // lane slots per row
     op.kw = ceil_div(op.units, 32);
     if (op.kw > kMegaConsumerWarps) return false;
     op.groups = std::min(kMegaMaxGroups, kMegaConsumerWarps / op.kw);
     auto a16 = [](int b) { return (b + 15) & ~15; };
-    op.woff_z = a16(op.rwc * op.wsize * 4);
-    op.woff_s = op.woff_z + a16(op.rwc * op.zsize * 4);
-    op.chunk_bytes = op.woff_s + a16(op.rwc * op.ssize * 2);
+    op.woff_z = a16(op.run_rows * op.wsize * 4);
+    op.woff_s = op.woff_z + a16(op.run_rows * op.zsize * 4);
+    op.chunk_bytes = op.woff_s + a16(op.run_rows * op.ssize * 2);
     return true;
+}
+
+// Layout of the peer-visible communication buffer of one rank (tensor parallel persistent kernel).
+struct CommLayout {
+    size_t done_off, recv_off, logits_off, x2_off, total;
+    int zones;
+};
+static CommLayout comm_layout(const Model* m)
+{
+    CommLayout L{};
+    auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+    const size_t nops = (size_t)5 * m->cfg.n_layers + 2;
+    L.zones = 4;
+    L.done_off = 0;
+    L.recv_off = up(nops * sizeof(unsigned int));
+    L.logits_off = L.recv_off + up((size_t)L.zones * m->tp * m->cfg.dim * sizeof(float));
+    L.x2_off = L.logits_off + up((size_t)m->cfg.vocab_size * sizeof(__half));
+    L.total = L.x2_off + up((size_t)m->cfg.dim * sizeof(__half));
+    return L;
 }
 
 static int build_mega(Model* m)
 {
     m->mega_built = true;
     m->mega_ok = false;
-    if (!m->use_mega || m->tp != 1) return ML2_OK;
+    if (!m->use_mega) return ML2_OK;
+    const bool tp = m->tp > 1;
+    if (tp && !m->comm_attached) return ML2_OK;   // without peer memory the graph + NCCL path is used
     const ml2_config& c = m->cfg;
     const int dim = c.dim, hs = m->head_size;
-    if (m->heads_local > m->ctx->sm_count || (hs / 2) % 4) return ML2_OK;
+    if (m->heads_local > m->ctx->sm_count || (hs / 2) % 4 || m->tp > 8) return ML2_OK;
+    const CommLayout CL = comm_layout(m);
+    auto peer = [&](int q, size_t off) { return static_cast<unsigned char*>(m->comm_peer[q]) + off; };
     std::vector<MegaOp> ops;
     const size_t kv_layer = (size_t)c.seq_len * m->dim_local;
     long long tiles_before = 0;
@@ -436,54 +476,96 @@ static int build_mega(Model* m)
         tiles_before += op.ntiles;
         ops.push_back(op);
     };
+    // residual stream: in place on one GPU; under tensor parallelism the update happens in the next norm
+    // operator's prologue and ping-pongs between two buffers (readers of the old one may still be running)
+    __half* x_cur = m->x;
+    __half* x_alt = tp ? reinterpret_cast<__half*>(peer(m->rank, CL.x2_off)) : nullptr;
+    int partial_ordinal = 0;
+    const float* pending_recv = nullptr;   // receive zone holding the partials not yet folded into x
+    auto norm_input = [&](MegaOp& op, const __half* gamma, bool first) {
+        op.gamma = gamma;
+        if (first) { op.pro = 2; op.in = x_cur; return; }
+        if (tp) {
+            op.pro = 3; op.tp = m->tp; op.in = x_cur; op.recv = pending_recv; op.x_next = x_alt;
+            std::swap(x_cur, x_alt);
+        } else {
+            op.pro = 1; op.in = x_cur;
+        }
+    };
+    auto partial_output = [&](MegaOp& op, int k_index) {
+        op.kind = MOP_PARTIAL;
+        op.tp = m->tp;
+        const size_t zone = (size_t)(partial_ordinal % CL.zones) * m->tp * dim * sizeof(float);
+        for (int q = 0; q < m->tp; ++q) {
+            op.peer_out[q] = reinterpret_cast<float*>(peer(q, CL.recv_off + zone + (size_t)m->rank * dim * sizeof(float)));
+            op.peer_done[q] = reinterpret_cast<unsigned int*>(peer(q, CL.done_off)) + k_index;
+        }
+        pending_recv = reinterpret_cast<const float*>(peer(m->rank, CL.recv_off + zone));
+        ++partial_ordinal;
+    };
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerW& L = m->layers[l];
         __half* kc = m->key_cache + (size_t)l * kv_layer;
         __half* vc = m->value_cache + (size_t)l * kv_layer;
         MegaOp q{};
-        q.kind = MOP_QKV; q.pro = (l == 0) ? 2 : 1; q.nmat = 3; q.nch = 2;
-        if (!mega_plan_op(q, 0, dim, m->dim_local)) return ML2_OK;
+        q.kind = MOP_QKV; q.nmat = 3;
+        if (!mega_plan_op(q, 0, dim, m->dim_local, true)) return ML2_OK;
+        norm_input(q, L.rms_att, l == 0);
         q.ntiles = 3 * (m->dim_local / 2 / q.rwc);
         q.mat[0] = qwp(L.q); q.mat[1] = qwp(L.k); q.mat[2] = qwp(L.v);
         q.out[0] = m->q; q.out[1] = kc; q.out[2] = vc;
-        q.in = m->x; q.gamma = L.rms_att;
         push(q);
         MegaOp a{};
-        a.kind = MOP_ATTN; a.in = m->q; a.out[0] = m->xb; a.kcache = kc; a.vcache = vc; a.ntiles = 0;
+        a.kind = MOP_ATTN; a.tp = 1; a.in = m->q; a.out[0] = m->xb; a.kcache = kc; a.vcache = vc; a.ntiles = 0;
         push(a);
         MegaOp o{};
-        o.kind = MOP_RESID; o.pro = 0; o.nmat = 1; o.nch = 1;
-        if (!mega_plan_op(o, 0, m->dim_local, dim)) return ML2_OK;
-        o.ntiles = ceil_div(dim, o.rwc);
-        o.mat[0] = qwp(L.o); o.out[0] = m->x; o.in = m->xb;
+        o.kind = MOP_RESID; o.pro = 0; o.nmat = 1;
+        if (!mega_plan_op(o, 0, m->dim_local, dim, false)) return ML2_OK;
+        o.ntiles = ceil_div(dim, o.run_rows);
+        o.mat[0] = qwp(L.o); o.out[0] = x_cur; o.in = m->xb;
+        if (tp) partial_output(o, (int)ops.size());
         push(o);
         MegaOp g{};
-        g.kind = MOP_SWIGLU; g.pro = 1; g.nmat = 2; g.nch = 2;
-        if (!mega_plan_op(g, 0, dim, m->hidden_local)) return ML2_OK;
+        g.kind = MOP_SWIGLU; g.nmat = 2;
+        if (!mega_plan_op(g, 0, dim, m->hidden_local, true)) return ML2_OK;
+        norm_input(g, L.rms_ffn, false);
         g.ntiles = ceil_div(m->hidden_local, g.rwc);
-        g.mat[0] = qwp(L.gate); g.mat[1] = qwp(L.up); g.out[0] = m->h; g.in = m->x; g.gamma = L.rms_ffn;
+        g.mat[0] = qwp(L.gate); g.mat[1] = qwp(L.up); g.out[0] = m->h;
         push(g);
         MegaOp d{};
-        d.kind = MOP_RESID; d.pro = 0; d.nmat = 1; d.nch = 1;
-        if (!mega_plan_op(d, 0, m->hidden_local, dim)) return ML2_OK;
-        d.ntiles = ceil_div(dim, d.rwc);
-        d.mat[0] = qwp(L.down); d.out[0] = m->x; d.in = m->h;
+        d.kind = MOP_RESID; d.pro = 0; d.nmat = 1;
+        if (!mega_plan_op(d, 0, m->hidden_local, dim, false)) return ML2_OK;
+        d.ntiles = ceil_div(dim, d.run_rows);
+        d.mat[0] = qwp(L.down); d.out[0] = x_cur; d.in = m->h;
+        if (tp) partial_output(d, (int)ops.size());
         push(d);
     }
     MegaOp cl{};
-    cl.kind = MOP_CLS; cl.pro = 1; cl.nmat = 1; cl.nch = 1;
-    if (!mega_plan_op(cl, 1, dim, m->vocab_local)) return ML2_OK;
+    cl.kind = MOP_CLS; cl.nmat = 1;
+    if (!mega_plan_op(cl, 1, dim, m->vocab_local, false)) return ML2_OK;
+    norm_input(cl, m->rms_final, false);
     cl.ntiles = ceil_div(m->vocab_local, cl.rwc);
     cl.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
-    cl.out[0] = m->logits; cl.in = m->x; cl.gamma = m->rms_final;
+    cl.out[0] = m->logits;
+    if (tp) {
+        cl.tp = m->tp;   // (norm_input set it already for the input side)
+        cl.out_row0 = m->vocab_row0;
+        for (int q = 0; q < m->tp; ++q) {
+            cl.peer_logits[q] = reinterpret_cast<__half*>(peer(q, CL.logits_off));
+            cl.peer_done[q] = reinterpret_cast<unsigned int*>(peer(q, CL.done_off)) + (int)ops.size();
+        }
+        m->logits_view = reinterpret_cast<__half*>(peer(m->rank, CL.logits_off));
+    } else {
+        m->logits_view = m->logits;
+    }
     push(cl);
     MegaOp am{};
-    am.kind = MOP_ARGMAX; am.ntiles = 0;
+    am.kind = MOP_ARGMAX; am.ntiles = 0; am.tp = 1;
     push(am);
 
     int slot = 0;
     for (const MegaOp& op : ops)
-        if (op.ntiles > 0) slot = std::max(slot, op.nch * op.chunk_bytes);
+        if (op.ntiles > 0) slot = std::max(slot, op.nruns * op.chunk_bytes);
     slot = (slot + 127) & ~127;
     const int widest = std::max(std::max(dim, m->hidden_local), m->dim_local);
     if (dim > 2 * 8 * kMegaConsumerWarps * 32) return ML2_OK;   // a normalised input vector is fetched as two pieces per thread
@@ -506,16 +588,19 @@ static int build_mega(Model* m)
     if (m->mega_ops) { cudaFree(m->mega_ops); m->mega_ops = nullptr; }
     ML2_CUDA(cudaMalloc(&m->mega_ops, ops.size() * sizeof(MegaOp)));
     ML2_CUDA(cudaMemcpyAsync(m->mega_ops, ops.data(), ops.size() * sizeof(MegaOp), cudaMemcpyHostToDevice, m->stream));
-    if (!m->mega_done) {
-        ML2_CUDA(cudaMalloc(&m->mega_done, ops.size() * sizeof(unsigned int)));
+    if (tp) {
+        m->mega_done_ptr = reinterpret_cast<unsigned int*>(peer(m->rank, CL.done_off));   // zeroed when the buffer was made
+    } else {
+        if (!m->mega_done) ML2_CUDA(cudaMalloc(&m->mega_done, ops.size() * sizeof(unsigned int)));
+        ML2_CUDA(cudaMemsetAsync(m->mega_done, 0, ops.size() * sizeof(unsigned int), m->stream));
+        m->mega_done_ptr = m->mega_done;
+        m->mega_seq = 0;
     }
-    ML2_CUDA(cudaMemsetAsync(m->mega_done, 0, ops.size() * sizeof(unsigned int), m->stream));
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     if (getenv("ML2_MEGA_PROF") && !m->mega_prof) {
         ML2_CUDA(cudaMalloc(&m->mega_prof, (size_t)m->mega_grid * 64 * sizeof(long long)));
         ML2_CUDA(cudaMemset(m->mega_prof, 0, (size_t)m->mega_grid * 64 * sizeof(long long)));
     }
-    m->mega_seq = 0;
     m->mega_ok = true;
     return ML2_OK;
 }
@@ -525,13 +610,13 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     MegaParams prm{};
     prm.ops = m->mega_ops;
     prm.nops = m->mega_nops;
-    prm.done = m->mega_done;
+    prm.done = m->mega_done_ptr;
     prm.status = m->ctx->status_dev;
     prm.rope_table = m->rope_table;
     prm.embed = m->embed;
     prm.x = m->x;
     prm.tokens = m->tokens;
-    prm.logits = m->logits;
+    prm.logits = m->logits_view;
     prm.pos = pos; prm.next_pos = next_pos; prm.write_token = write_token;
     prm.seq_no = ++m->mega_seq;
     prm.dim = m->cfg.dim; prm.head_size = m->head_size; prm.heads_local = m->heads_local;
@@ -624,6 +709,11 @@ int ml2_model_create(ml2_ctx* h, const ml2_config* cfg, int tp_size, int tp_rank
     if (tp_size > 1) {
         if ((rc = dev_alloc(m, (void**)&m->partial, (size_t)c.dim * sizeof(float)))) return rc;
         if ((rc = dev_alloc(m, (void**)&m->logits_local, (size_t)m->vocab_local * sizeof(__half)))) return rc;
+        {   // peer-visible buffer of the persistent kernel (counters, receive zones, logits, second residual buffer)
+            const CommLayout CL = comm_layout(m);
+            ML2_CUDA(cudaMalloc(&m->comm_local, CL.total));
+            ML2_CUDA(cudaMemsetAsync(m->comm_local, 0, CL.total, m->stream));
+        }
         if ((rc = nccl_load())) return rc;
         ncclUniqueId id;
         memcpy(&id, nccl_id128, sizeof(id));
@@ -654,6 +744,9 @@ int ml2_model_destroy(ml2_model* h)
     if (m->exec) cudaGraphExecDestroy(m->exec);
     if (m->graph) cudaGraphDestroy(m->graph);
     if (m->comm) g_nccl.CommDestroy(m->comm);
+    for (int q = 0; q < m->tp; ++q)
+        if (m->comm_attached && q != m->rank && m->comm_peer[q]) cudaIpcCloseMemHandle(m->comm_peer[q]);
+    if (m->comm_local) cudaFree(m->comm_local);
     if (m->mega_ops) cudaFree(m->mega_ops);
     if (m->mega_done) cudaFree(m->mega_done);
     for (void* p : m->owned) cudaFree(p);
@@ -857,7 +950,8 @@ int ml2_model_read_logits(ml2_model* h, void* logits_host_f16)
 {
     Model* m = reinterpret_cast<Model*>(h);
     if (!m || !logits_host_f16) return fail(ML2_E_INVALID, "read_logits: null argument");
-    ML2_CUDA(cudaMemcpyAsync(logits_host_f16, m->logits, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, m->stream));
+    const __half* src = (m->mega_ok && m->logits_view) ? m->logits_view : m->logits;
+    ML2_CUDA(cudaMemcpyAsync(logits_host_f16, src, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, m->stream));
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     return ML2_OK;
 }
@@ -868,6 +962,45 @@ int ml2_model_debug_prof(ml2_model* h, long long* out, int n)
     if (!m || !out || !m->mega_prof) return fail(ML2_E_STATE, "no profile buffer (set ML2_MEGA_PROF=1 before the first forward)");
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     ML2_CUDA(cudaMemcpy(out, m->mega_prof, (size_t)std::min(n, m->mega_grid * 64) * sizeof(long long), cudaMemcpyDeviceToHost));
+    return ML2_OK;
+}
+
+int ml2_model_comm_handle(ml2_model* h, void* out64)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !out64) return fail(ML2_E_INVALID, "comm_handle: null argument");
+    if (m->tp < 2 || !m->comm_local) return fail(ML2_E_STATE, "comm_handle: the model is not tensor parallel");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t size");
+    cudaIpcMemHandle_t hd;
+    ML2_CUDA(cudaIpcGetMemHandle(&hd, m->comm_local));
+    memcpy(out64, &hd, sizeof(hd));
+    return ML2_OK;
+}
+
+int ml2_model_comm_attach(ml2_model* h, const void* handles, int n)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !handles) return fail(ML2_E_INVALID, "comm_attach: null argument");
+    if (m->tp < 2 || !m->comm_local) return fail(ML2_E_STATE, "comm_attach: the model is not tensor parallel");
+    if (n != m->tp || n > 8) return fail(ML2_E_INVALID, "comm_attach: %d handles for %d ranks (at most 8)", n, m->tp);
+    if (m->comm_attached) return fail(ML2_E_STATE, "comm_attach: already attached");
+    ML2_CUDA(cudaSetDevice(m->ctx->device));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    for (int q = 0; q < n; ++q) {
+        if (q == m->rank) { m->comm_peer[q] = m->comm_local; continue; }
+        cudaIpcMemHandle_t hd;
+        memcpy(&hd, static_cast<const char*>(handles) + (size_t)q * 64, sizeof(hd));
+        void* ptr = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&ptr, hd, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int r = 0; r < q; ++r)
+                if (r != m->rank && m->comm_peer[r]) { cudaIpcCloseMemHandle(m->comm_peer[r]); m->comm_peer[r] = nullptr; }
+            return fail(ML2_E_CUDA, "comm_attach: cudaIpcOpenMemHandle(rank %d): %s", q, cudaGetErrorString(e));
+        }
+        m->comm_peer[q] = ptr;
+    }
+    m->comm_attached = true;
+    m->mega_built = false;
     return ML2_OK;
 }
 

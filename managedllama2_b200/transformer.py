@@ -191,6 +191,28 @@ class Transformer:
         _lib.check(_lib.load().ml2_nccl_unique_id(buf))
         return buf.raw
 
+    # -- tensor-parallel persistent kernel: peer memory -----------------------------------------------
+    def comm_handle(self):
+        """64-byte CUDA IPC handle of this rank's peer-visible buffer (tensor parallel models only)."""
+        buf = ctypes.create_string_buffer(64)
+        _lib.check(self.lib.ml2_model_comm_handle(self.handle, buf))
+        return buf.raw
+
+    def attach_peers(self, handles):
+        """``handles``: the comm_handle() bytes of every rank, in rank order. Enables the one-launch-per-token path."""
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.tp_size
+        _lib.check(self.lib.ml2_model_comm_attach(self.handle, ctypes.create_string_buffer(blob, len(blob)), self.tp_size))
+
+    def attach_peers_with(self, dist):
+        """Exchanges the handles over an initialised ``torch.distributed`` group and attaches them."""
+        import torch
+        mine = torch.frombuffer(bytearray(self.comm_handle()), dtype=torch.uint8).cuda()
+        allh = [torch.empty_like(mine) for _ in range(self.tp_size)]
+        dist.all_gather(allh, mine)
+        self.attach_peers([bytes(t.cpu().numpy().tobytes()) for t in allh])
+        dist.barrier()
+
     # -- reference API ---------------------------------------------------------------------------
     def Forward(self, position, nextPosition, generateToken=True):
         _lib.check(self.lib.ml2_model_forward(self.handle, position, nextPosition, 1 if generateToken else 0))

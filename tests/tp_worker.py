@@ -27,6 +27,8 @@ def main():
     ctx = ml2.CudaContext(local)
     w = ml2.synthetic_weights(ctx, cfg, seed=21, tp_size=world, tp_rank=rank)
     tr = ml2.Transformer(cfg, w, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
+    if os.environ.get("ML2_TP_FUSED", "1") == "1":
+        tr.attach_peers_with(dist)   # one persistent kernel per token, all-reduce over peer memory
     toks = [5, 99, 256, 31]
     tr.set_tokens(np.array(toks, dtype=np.int32))
     cpu = None
