@@ -21,6 +21,13 @@
 
 #include "stream_matvec.cuh"
 
+#ifndef ML2_CW
+#define ML2_CW 21
+#endif
+#ifndef ML2_MULTI
+#define ML2_MULTI 1
+#endif
+
 namespace ml2 {
 
 enum MegaOpKind : int { MOP_QKV = 0, MOP_ATTN = 1, MOP_RESID = 2, MOP_SWIGLU = 3, MOP_CLS = 4, MOP_ARGMAX = 5, MOP_PARTIAL = 6 };
@@ -41,7 +48,7 @@ struct MegaOp {
     int rot;                 // rotation of the tile -> CTA assignment
     int tp;                  // ranks summed into the input (pro 3) / receiving the output (MOP_PARTIAL, sharded MOP_CLS)
     int out_row0;            // sharded classifier: first vocabulary row of this rank
-    int pad;
+    int passes;              // a group covers a row in `passes` sweeps of kw * 32 lane slots (1: input slice stays in registers)
     QWPtrs mat[3];
     __half* out[3];
     float* out_f32;
@@ -76,7 +83,7 @@ struct MegaParams {
     long long* prof;           // optional [gridDim.x][64] cycle counters (diagnostics), may be null
 };
 
-constexpr int kMegaConsumerWarps = 20;
+constexpr int kMegaConsumerWarps = ML2_CW;
 constexpr int kMegaFinalWarps = 2;
 constexpr int kMegaWarps = kMegaConsumerWarps + 1 + kMegaFinalWarps;
 constexpr int kMegaThreads = kMegaWarps * 32;
@@ -219,6 +226,175 @@ __device__ __forceinline__ float slice_sumsq(const uint32_t (&xr)[NX / 2])
         ss = fmaf(b, b, ss);
     }
     return warp_sum(ss);
+}
+
+// Four rows of one lane slot: dequantise-and-multiply against the prepared slice `xq`; zero point and scale are
+// applied once per row (aw / az / as: shared-memory addresses of the lane's weight vector, zero word and scale of row 0).
+__device__ __forceinline__ void mega_int4_rows(const XSlice& xq, uint32_t aw, uint32_t az, uint32_t as, uint32_t w_row, uint32_t z_row,
+                                               uint32_t s_row, int zshift, bool act, float (&v)[4])
+{
+    uint4 wv[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(wv[r].x), "=r"(wv[r].y), "=r"(wv[r].z), "=r"(wv[r].w)
+                     : "r"(aw + r * w_row));
+    // two accumulators per row (A: nibbles 0, 2, 4, 6; B: the odd ones, scaled by 16), four rows in flight
+    float A[4], B[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        A[r] = xq.a0;
+        B[r] = xq.b0;
+        word_dot(wv[r].x, xq.xp + 0, A[r], B[r], A[r]);
+        word_dot(wv[r].y, xq.xp + 4, A[r], B[r], A[r]);
+        word_dot(wv[r].z, xq.xp + 8, A[r], B[r], A[r]);
+        word_dot(wv[r].w, xq.xp + 12, A[r], B[r], A[r]);
+    }
+    // zero point and scale are fetched after the products: they are needed only now, and eight fewer registers are
+    // live during the inner loop
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        uint32_t zw;
+        unsigned short sc;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw) : "r"(az + r * z_row));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc) : "r"(as + r * s_row));
+        const float zf = (float)((zw >> zshift) & 0xFu);
+        const float t = fmaf(B[r], 0.0625f, A[r]);
+        const float res = half_bits_to_float(sc) * fmaf(-zf, xq.c1, t);
+        v[r] = act ? res : 0.f;
+    }
+}
+
+constexpr int kSliceVecs = 5;   // 16-byte vectors of a prepared slice parked in shared memory
+
+// Prepared slice of lane slot `sidx` -> table [kSliceVecs][tab_n] (xp: 4 vectors, start values: 1).
+__device__ __forceinline__ void mega_store_slice(uint4* tab, int tab_n, int sidx, const XSlice& t)
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q) tab[q * tab_n + sidx] = make_uint4(t.xp[4 * q], t.xp[4 * q + 1], t.xp[4 * q + 2], t.xp[4 * q + 3]);
+    tab[(kSliceVecs - 1) * tab_n + sidx] = make_uint4(__float_as_uint(t.a0), __float_as_uint(t.b0), __float_as_uint(t.c1), 0u);
+}
+
+__device__ __forceinline__ void mega_load_slice_tab(uint32_t ta, uint32_t tstep, XSlice& xt)
+{
+    float pad;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(xt.xp[4 * q]), "=r"(xt.xp[4 * q + 1]), "=r"(xt.xp[4 * q + 2]), "=r"(xt.xp[4 * q + 3])
+                     : "r"(ta + q * tstep));
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(xt.a0), "=f"(xt.b0), "=f"(xt.c1), "=f"(pad) : "r"(ta + (kSliceVecs - 1) * tstep));
+}
+
+// Shared-memory objects of the kernel that the multi-sweep consumer needs.
+struct MegaShared {
+    unsigned char* smem;     // ring, then the scratch area
+    uint64_t* full_bar;
+    uint64_t* empty_bar;
+    uint64_t* done_bar;
+    uint64_t* free_bar;
+    float* red;              // [kMegaRedSlots][kMaxKW][kMegaMaxRows]
+    unsigned int* abort_flag;
+    DeviceStatus* status;
+    int nstage, slot_bytes;
+};
+
+// Consumer side of an int4 operator whose rows are wider than one sweep of a group (op.passes > 1; plain input).
+// Every lane slot's prepared slice is built once per operator and parked in shared memory; a group of kw warps sweeps
+// a tile `passes` times, reloading the lane's slice per sweep, so that groups * kw warps stay busy where a single
+// sweep would tie most of the warps to one row. A loop of its own, apart from the single-sweep loop of the kernel.
+__device__ __forceinline__ void mega_multisweep_op(const MegaOp& op, int k, const MegaShared& sh, int first, int cnt, uint32_t n_base,
+                                                   int st_base, uint32_t ph_base)
+{
+    constexpr int kConsThreads = kMegaConsumerWarps * 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ncta = gridDim.x;
+    const int npass = op.passes;
+    const int stride = op.kw * 32;
+    const int tab_n = stride * npass;
+    uint4* s_tab = reinterpret_cast<uint4*>(sh.smem + (size_t)sh.nstage * sh.slot_bytes);
+    for (int sidx = tid; sidx < tab_n; sidx += kConsThreads) {
+        uint32_t xr[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xr[i] = 0u;
+        if (sidx < op.units) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 t = *reinterpret_cast<const uint4*>(op.in + (size_t)sidx * 32 + v * 8);
+                xr[4 * v] = t.x; xr[4 * v + 1] = t.y; xr[4 * v + 2] = t.z; xr[4 * v + 3] = t.w;
+            }
+        }
+        XSlice t;
+        make_xslice(xr, t);
+        mega_store_slice(s_tab, tab_n, sidx, t);
+    }
+    named_bar_sync(1, kConsThreads);
+
+    const int group = warp / op.kw;
+    const int kw_id = warp - group * op.kw;
+    if (group >= op.groups) return;
+    const int u = kw_id * 32 + lane;
+    const uint32_t w_row = (uint32_t)op.wsize * 4u, z_row = (uint32_t)op.zsize * 4u, s_row = (uint32_t)op.ssize * 2u;
+    const uint32_t ring = smem_u32(sh.smem);
+    const uint32_t tab = smem_u32(s_tab), tstep = (uint32_t)tab_n * 16u;
+    const uint32_t my_arrive = (kw_id == 0) ? (kBarCount - (uint32_t)op.kw + 1u) : 1u;
+    const bool writer = (lane & 7) == 0 && (lane >> 3) < op.rwc;
+    int st = st_base + group;
+    uint32_t ph = ph_base;
+    while (st >= sh.nstage) { st -= sh.nstage; ph ^= 1u; }
+    for (int i = group; i < cnt; i += op.groups) {
+        const uint32_t n = n_base + (uint32_t)i;
+        wait_or_abort(&sh.full_bar[st], ph, sh.abort_flag, sh.status, 2u, k);
+        const int slot = (int)(n % kMegaRedSlots);
+        float* red = sh.red + (size_t)slot * (kMaxKW * kMegaMaxRows);
+        bool slot_ready = n < (uint32_t)kMegaRedSlots;
+        float resid[2] = {0.f, 0.f};
+        if (op.kind == MOP_RESID && kw_id == 0 && writer) {
+            const int tile = first + i * ncta;
+            for (int c = 0; c < op.nch; ++c) {
+                const int row = (tile * op.nch + c) * op.rwc + (lane >> 3);
+                if (row < op.cols) resid[c] = __half2float(op.out[0][row]);
+            }
+        }
+        for (int c = 0; c < op.nch; ++c) {
+            const int trow = c * op.rwc;
+            const int run = trow / op.run_rows;
+            const int rin0 = trow - run * op.run_rows;
+            const uint32_t cbase = ring + (uint32_t)st * sh.slot_bytes + (uint32_t)run * op.chunk_bytes;
+            const uint32_t cw = cbase + (uint32_t)rin0 * w_row;
+            const uint32_t cz = cbase + op.woff_z + (uint32_t)rin0 * z_row;
+            const uint32_t cs = cbase + op.woff_s + (uint32_t)rin0 * s_row;
+            float tot[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < npass; ++j) {
+                const int uj = u + j * stride;
+                const bool act = uj < op.units;
+                const int ua = act ? uj : 0;
+                const int g = ua >> 2;
+                XSlice xt;
+                mega_load_slice_tab(tab + (uint32_t)uj * 16u, tstep, xt);
+                float v[4];
+                mega_int4_rows(xt, cw + (uint32_t)ua * 16u, cz + (uint32_t)(g >> 3) * 4u, cs + (uint32_t)g * 2u, w_row, z_row, s_row,
+                               (g & 7) * 4, act, v);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) tot[r] += v[r];
+            }
+            if (c == op.nch - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive_n(&sh.empty_bar[st], my_arrive);
+            }
+            transpose_reduce<4>(tot, lane);
+            if (!slot_ready) {
+                wait_or_abort(&sh.free_bar[slot], ((n / kMegaRedSlots) - 1u) & 1u, sh.abort_flag, sh.status, 4u, k);
+                slot_ready = true;
+            }
+            if (writer) red[kw_id * kMegaMaxRows + c * op.rwc + (lane >> 3)] = tot[0];
+            if (op.kind == MOP_RESID && kw_id == 0 && writer) red[op.kw * kMegaMaxRows + c * op.rwc + (lane >> 3)] = resid[c];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_n(&sh.done_bar[slot], my_arrive);
+        st += op.groups;
+        while (st >= sh.nstage) { st -= sh.nstage; ph ^= 1u; }
+    }
 }
 
 // kProf adds cycle counters around the waits (diagnostics); the production instantiation carries none.
@@ -561,6 +737,21 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         }
         wait_dependency();
 
+        if (ML2_MULTI && op.passes > 1) {
+            MegaShared sh;
+            sh.smem = smem_raw; sh.full_bar = full_bar; sh.empty_bar = empty_bar; sh.done_bar = done_bar; sh.free_bar = free_bar;
+            sh.red = &s_red[0][0][0]; sh.abort_flag = &s_abort;
+            sh.status = p.status; sh.nstage = p.nstage; sh.slot_bytes = p.slot_bytes;
+            const long long trun0 = now();
+            mega_multisweep_op(op, k, sh, first, cnt, n_base, st_base, ph_base);
+            tk_run[kk] += now() - trun0;
+            n_base += (uint32_t)cnt;
+            st_base += cnt % p.nstage;
+            ph_base ^= (uint32_t)(cnt / p.nstage) & 1u;
+            if (st_base >= p.nstage) { st_base -= p.nstage; ph_base ^= 1u; }
+            continue;
+        }
+
         XSlice xs;
         {
             const __half* src = op.in;
@@ -701,35 +892,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
                 if (p.debug & 1) {
                 } else if (is_int4) {
-                    uint4 wv[4];
-                    uint32_t zw[4];
-                    unsigned short sc[4];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(wv[r].x), "=r"(wv[r].y), "=r"(wv[r].z), "=r"(wv[r].w)
-                                     : "r"(cw + w_off + r * w_row));
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw[r]) : "r"(cz + z_off + r * z_row));
-                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc[r]) : "r"(cs + s_off + r * s_row));
-                    }
-                    float A[4], B[4], D[4];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        A[r] = xs.a0;
-                        B[r] = xs.b0;
-                        D[r] = xs.d0;
-                        word_dot(wv[r].x, xs.xp + 0, xs.xf + 0, A[r], B[r], D[r]);
-                        word_dot(wv[r].y, xs.xp + 4, xs.xf + 2, A[r], B[r], D[r]);
-                        word_dot(wv[r].z, xs.xp + 8, xs.xf + 4, A[r], B[r], D[r]);
-                        word_dot(wv[r].w, xs.xp + 12, xs.xf + 6, A[r], B[r], D[r]);
-                    }
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const float zf = (float)((zw[r] >> zshift) & 0xFu);
-                        const float t = fmaf(B[r], 0.0625f, A[r]) + D[r];
-                        const float res = half_bits_to_float(sc[r]) * fmaf(-zf, xs.c1, t);
-                        v[r] = active ? res : 0.f;
-                    }
+                    mega_int4_rows(xs, cw + w_off, cz + z_off, cs + s_off, w_row, z_row, s_row, zshift, active, v);
                 } else {
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {

@@ -397,7 +397,7 @@ static double qweight_bytes(int rows, int cols)
 }
 
 // ---- persistent per-token kernel: operator list and launch ------------------------------------------------------
-static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, bool paired)
+static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, bool paired, bool plain_input = false)
 {
     op.fmt = fmt;
     op.rows = rows;
@@ -427,9 +427,27 @@ static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, bool paired)
     }
     if (cols % op.run_rows) return false;
     op.units = fmt == 0 ? op.wsize / 4 : op.wsize / 8;   // lane slots per row
-    op.kw = ceil_div(op.units, 32);
-    if (op.kw > kMegaConsumerWarps) return false;
-    op.groups = std::min(kMegaMaxGroups, kMegaConsumerWarps / op.kw);
+    // Warps per group and sweeps per row: a group of kw warps covers a row in `passes` sweeps of kw * 32 lane slots
+    // and `groups` groups work side by side, so the rate is proportional to groups / passes. One sweep keeps the
+    // input slice in registers; more sweeps reload prepared slices from shared memory (int4 operators whose input
+    // needs no normalisation only), which keeps all warps busy when a row is wider than a third of the lanes.
+    op.kw = 0;
+    op.passes = 1;
+    op.groups = 0;
+    const bool multi = fmt == 0 && plain_input && !getenv("ML2_MEGA_ONE_PASS");
+    for (int kw = 1; kw <= kMegaConsumerWarps; ++kw) {
+        const int passes = ceil_div(op.units, 32 * kw);
+        if (passes > (multi ? 4 : 1)) continue;
+        const int groups = std::min(kMegaMaxGroups, kMegaConsumerWarps / kw);
+        // better: higher groups / passes; then fewer sweeps
+        const long lhs = (long)groups * op.passes, rhs = (long)op.groups * passes;
+        if (op.kw == 0 || lhs > rhs || (lhs == rhs && passes < op.passes)) {
+            op.kw = kw;
+            op.passes = passes;
+            op.groups = groups;
+        }
+    }
+    if (op.kw == 0) return false;
     auto a16 = [](int b) { return (b + 15) & ~15; };
     op.woff_z = a16(op.run_rows * op.wsize * 4);
     op.woff_s = op.woff_z + a16(op.run_rows * op.zsize * 4);
@@ -520,7 +538,7 @@ static int build_mega(Model* m)
         push(a);
         MegaOp o{};
         o.kind = MOP_RESID; o.pro = 0; o.nmat = 1;
-        if (!mega_plan_op(o, 0, m->dim_local, dim, false)) return ML2_OK;
+        if (!mega_plan_op(o, 0, m->dim_local, dim, false, true)) return ML2_OK;
         o.ntiles = ceil_div(dim, o.run_rows);
         o.mat[0] = qwp(L.o); o.out[0] = x_cur; o.in = m->xb;
         if (tp) partial_output(o, (int)ops.size());
@@ -534,7 +552,7 @@ static int build_mega(Model* m)
         push(g);
         MegaOp d{};
         d.kind = MOP_RESID; d.pro = 0; d.nmat = 1;
-        if (!mega_plan_op(d, 0, m->hidden_local, dim, false)) return ML2_OK;
+        if (!mega_plan_op(d, 0, m->hidden_local, dim, false, true)) return ML2_OK;
         d.ntiles = ceil_div(dim, d.run_rows);
         d.mat[0] = qwp(L.down); d.out[0] = x_cur; d.in = m->h;
         if (tp) partial_output(d, (int)ops.size());
@@ -567,9 +585,15 @@ static int build_mega(Model* m)
     for (const MegaOp& op : ops)
         if (op.ntiles > 0) slot = std::max(slot, op.nruns * op.chunk_bytes);
     slot = (slot + 127) & ~127;
-    const int widest = std::max(std::max(dim, m->hidden_local), m->dim_local);
+    // scratch beside the ring: attention scores, or the staged input vector of a single-sweep operator, or the
+    // prepared-slice table of a multi-sweep operator (7 vectors of 16 bytes per lane slot)
+    int scratch = c.seq_len * 4;
+    for (const MegaOp& op : ops) {
+        if (op.ntiles == 0) continue;
+        scratch = std::max(scratch, op.passes > 1 ? op.kw * 32 * op.passes * kSliceVecs * 16 : op.rows * 2);
+    }
     if (dim > 2 * 8 * kMegaConsumerWarps * 32) return ML2_OK;   // a normalised input vector is fetched as two pieces per thread
-    const int att_bytes = (std::max(c.seq_len * 4, widest * 2) + 127) & ~127;
+    const int att_bytes = (scratch + 127) & ~127;
     const int budget = 200 * 1024;
     int nstage = (budget - att_bytes) / slot;
     if (nstage > kMegaMaxStages) nstage = kMegaMaxStages;
