@@ -448,48 +448,73 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         int st = 0;
         uint32_t ph = 0;      // parity of (uses of this stage so far)
         bool wrapped = false;
+        long long tp_wait = 0, tp_all0 = now();
+        const bool nocopy = (p.debug & 8) != 0;
         for (int k = 0; k < p.nops; ++k) {
-            const MegaOp op = p.ops[k];
-            if (op.ntiles == 0) continue;
-            const int first = my_first(op), cnt = my_count(op, first);
+            // The per-tile chain of this warp bounds the streaming rate of the CTA: everything that does not change
+            // from tile to tile is read once per operator into registers, tile addresses advance by increments.
+            const MegaOp* gp = p.ops + k;
+            const int ntiles = gp->ntiles;
+            if (ntiles == 0) continue;
+            const int kind = gp->kind, cols = gp->cols, rwc = gp->rwc, nruns = gp->nruns;
+            const bool int4 = gp->fmt == 0;
+            const bool paired = kind == MOP_SWIGLU || kind == MOP_QKV;
+            const int rr = paired ? rwc : gp->run_rows;             // rows of one run
+            const uint32_t wrow = (uint32_t)gp->wsize * 4u, zrow = int4 ? (uint32_t)gp->zsize * 4u : 0u, srow = int4 ? (uint32_t)gp->ssize * 2u : 0u;
+            const uint32_t woff_z = gp->woff_z, woff_s = gp->woff_s;
+            const uint32_t lane_off = (uint32_t)lane * (uint32_t)gp->chunk_bytes;
+            int first = (cta - gp->rot) % ncta;
+            if (first < 0) first += ncta;
+            const int cnt = ntiles > first ? (ntiles - 1 - first) / ncta + 1 : 0;
+            // QKV: tile -> (matrix, pair of row blocks); the two runs of a tile are rotate-half partners
+            const int half = p.head_size >> 1;
+            const int ppm = paired ? (cols >> 1) / rwc : 1, pph = paired ? half / rwc : 1;
+            int qm = 0, qpp = 0;
+            if (kind == MOP_QKV) { qm = first / ppm; qpp = first - qm * ppm; }
+            QWPtrs q = gp->mat[kind == MOP_SWIGLU ? (lane & 1) : (qm < 2 ? qm : 2)];
             int tile = first;
             for (int i = 0; i < cnt; ++i, tile += ncta) {
                 if (wrapped) {
+                    const long long tw0 = now();
                     if (lane == 0) wait_parked_or_abort(&empty_bar[st], ph ^ 1u, &s_abort, p.status, 1u, k);
                     __syncwarp();
+                    tp_wait += now() - tw0;
                 }
-                unsigned char* sbase = smem_raw + (size_t)st * p.slot_bytes;
-                MegaChunk c{0, 0, 0};
-                if (lane < op.nruns) c = mega_run(op, p.head_size, tile, lane);
-                const QWPtrs q = op.mat[c.m < op.nmat ? c.m : 0];
-                const uint32_t* gw = q.w + (size_t)c.row0 * op.wsize;
-                const uint32_t bw = (uint32_t)c.nrows * op.wsize * 4u;
-                const uint32_t* gz = nullptr;
-                const __half* gs = nullptr;
-                uint32_t bz = 0, bs = 0;
-                if (op.fmt == 0) {
-                    gz = q.z + (size_t)c.row0 * op.zsize;
-                    gs = q.s + (size_t)c.row0 * op.ssize;
-                    bz = (uint32_t)c.nrows * op.zsize * 4u;
-                    bs = (uint32_t)c.nrows * op.ssize * 2u;
+                int row0;
+                if (kind == MOP_QKV) {
+                    const int head = qpp / pph;
+                    row0 = head * p.head_size + (qpp - head * pph) * rwc + (lane & 1) * half;
+                } else {
+                    row0 = tile * rr;
                 }
-                const bool live = c.nrows > 0;
-                uint32_t tx = live ? (bw + bz + bs) : 0u;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
-                const bool nocopy = (p.debug & 8) != 0;
-                if (lane == 0) mbar_arrive_expect_tx(&full_bar[st], nocopy ? 0u : tx);
+                int nrows = cols - row0;
+                nrows = nrows < 0 ? 0 : (nrows > rr ? rr : nrows);
+                const uint32_t bw = (uint32_t)nrows * wrow, bz = (uint32_t)nrows * zrow, bs = (uint32_t)nrows * srow;
+                // every run of a tile holds the same number of rows (the operator plan admits full tiles only)
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[st], nocopy ? 0u : (uint32_t)nruns * (bw + bz + bs));
                 __syncwarp();
-                if (live && !nocopy) {
-                    unsigned char* cb = sbase + (size_t)lane * op.chunk_bytes;
-                    bulk_g2s(cb, gw, bw, &full_bar[st], pol);
-                    if (op.fmt == 0) {
-                        bulk_g2s(cb + op.woff_z, gz, bz, &full_bar[st], pol);
-                        bulk_g2s(cb + op.woff_s, gs, bs, &full_bar[st], pol);
+                if (lane < nruns && nrows > 0 && !nocopy) {
+                    unsigned char* cb = smem_raw + (size_t)st * p.slot_bytes + lane_off;
+                    bulk_g2s(cb, q.w + (size_t)row0 * (wrow >> 2), bw, &full_bar[st], pol);
+                    if (int4) {
+                        bulk_g2s(cb + woff_z, q.z + (size_t)row0 * (zrow >> 2), bz, &full_bar[st], pol);
+                        bulk_g2s(cb + woff_s, q.s + (size_t)row0 * (srow >> 1), bs, &full_bar[st], pol);
+                    }
+                }
+                if (kind == MOP_QKV) {
+                    qpp += ncta;
+                    if (qpp >= ppm) {
+                        do { qpp -= ppm; ++qm; } while (qpp >= ppm);
+                        q = gp->mat[qm < 2 ? qm : 2];
                     }
                 }
                 if (++st == p.nstage) { st = 0; ph ^= 1u; wrapped = true; }
             }
+        }
+        if (kProf && p.prof && lane == 0) {
+            long long* o = p.prof + (size_t)cta * 64;
+            o[32] = now() - tp_all0;
+            o[33] = tp_wait;
         }
         return;
     }
@@ -498,94 +523,131 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         // ================= finalizers: fixed-order sum over k-warps + operator tail ========================
         const int fw = warp - kMegaConsumerWarps - 1;
         uint32_t n = 0;
+        long long tf_wait = 0, tf_all0 = now();
         for (int k = 0; k < p.nops; ++k) {
-            const MegaOp op = p.ops[k];
-            if (op.ntiles == 0) continue;   // attention / argmax are published by the consumers
-            const int first = my_first(op), cnt = my_count(op, first);
+            // As in the producer, the operator's invariants sit in registers and nothing is divided per tile.
+            const MegaOp* gp = p.ops + k;
+            const int ntiles = gp->ntiles;
+            if (ntiles == 0) continue;   // attention / argmax are published by the consumers
+            const int kind = gp->kind, cols = gp->cols, rwc = gp->rwc, kw = gp->kw, tp = gp->tp;
+            const bool paired = kind == MOP_SWIGLU || kind == MOP_QKV;
+            int first = (cta - gp->rot) % ncta;
+            if (first < 0) first += ncta;
+            const int cnt = ntiles > first ? (ntiles - 1 - first) / ncta + 1 : 0;
+            const int half = p.head_size >> 1;
+            const int ppm = paired ? (cols >> 1) / rwc : 1, pph = paired ? half / rwc : 1;
+            int qm = 0, qpp = 0;
+            if (kind == MOP_QKV) { qm = first / ppm; qpp = first - qm * ppm; }
+            // lane roles: paired tiles use lanes [0, rwc) (one output row pair each); other tiles one lane per row
+            const int nrow = paired ? rwc : gp->nch * rwc;
+            const int roff = lane;                              // index of this lane's row inside the partial slot
+            __half* const out0 = gp->out[0];
+            __half* out_m = kind == MOP_QKV ? gp->out[qm < 2 ? qm : 2] : out0;
+            const int rows_per_tile = paired ? rwc : gp->nch * rwc;
             for (int i = 0; i < cnt; ++i, ++n) {
-                if ((int)(n % kMegaFinalWarps) != fw) continue;
-                const int tile = first + i * ncta;
-                const int slot = (int)(n % kMegaRedSlots);
-                const float* red = &s_red[slot][0][0];
-                if (p.debug & 4) {
-                    wait_parked_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1u, &s_abort, p.status, 3u, k);
-                } else if (op.kind == MOP_SWIGLU || op.kind == MOP_QKV) {
-                    const bool mine = lane < op.rwc;
-                    MegaChunk ca{0, 0, 0}, cb{0, 0, 0};
-                    if (mine) { ca = mega_chunk(op, p.head_size, tile, 0); cb = mega_chunk(op, p.head_size, tile, 1); }
-                    const int r = lane;
-                    float2 cs = make_float2(1.f, 0.f);
-                    if (op.kind == MOP_QKV && mine && r < ca.nrows && ca.m < 2)
-                        cs = p.rope_table[(size_t)p.pos * (p.head_size >> 1) + (ca.row0 + r) % p.head_size];
-                    wait_parked_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1u, &s_abort, p.status, 3u, k);
-                    if (mine && r < ca.nrows) {
-                        float sa = 0.f, sb = 0.f;
-                        for (int w = 0; w < op.kw; ++w) {
-                            sa += red[w * kMegaMaxRows + r];
-                            sb += red[w * kMegaMaxRows + op.rwc + r];
-                        }
-                        if (op.kind == MOP_SWIGLU) {
-                            float val = sa;                       // native/mat_vec_kernel.cu:218-222
-                            val *= 1.0f / (1.0f + expf(-val));
-                            val *= sb;
-                            op.out[0][ca.row0 + r] = __float2half_rn(val);
+                const bool take = (int)(n % kMegaFinalWarps) == fw;
+                if (take) {
+                    const int tile = first + i * ncta;
+                    const int slot = (int)(n % kMegaRedSlots);
+                    const float* red = &s_red[slot][0][0];
+                    const uint32_t par = (n / kMegaRedSlots) & 1u;
+                    if (p.debug & 4) {
+                        wait_parked_or_abort(&done_bar[slot], par, &s_abort, p.status, 3u, k);
+                    } else if (paired) {
+                        // rows ra (chunk 0) and rb (chunk 1) of this lane
+                        int ra, rb;
+                        if (kind == MOP_QKV) {
+                            const int head = qpp / pph;
+                            ra = head * p.head_size + (qpp - head * pph) * rwc + lane;
+                            rb = ra + half;
                         } else {
-                            __half* o = op.out[ca.m];
-                            if (ca.m > 0) o += (long long)p.pos * p.kv_row_stride;
-                            if (ca.m < 2) {
-                                // fp16 store of the mat-vec (native/mat_vec_kernel.cu:175), then RoPE on the rounded
-                                // values (native/rope_kernel.cu:15-25)
-                                const float a0 = __half2float(__float2half_rn(sa));
-                                const float b0 = __half2float(__float2half_rn(sb));
-                                o[ca.row0 + r] = __float2half_rn(a0 * cs.x - b0 * cs.y);
-                                o[cb.row0 + r] = __float2half_rn(a0 * cs.y + b0 * cs.x);
+                            ra = rb = tile * rwc + lane;
+                        }
+                        const bool mine = lane < rwc && ra < cols;
+                        float2 cs = make_float2(1.f, 0.f);
+                        if (kind == MOP_QKV && mine && qm < 2) cs = p.rope_table[(size_t)p.pos * half + ra % p.head_size];
+                        const long long tw0 = now();
+                        wait_parked_or_abort(&done_bar[slot], par, &s_abort, p.status, 3u, k);
+                        tf_wait += now() - tw0;
+                        if (mine) {
+                            float sa = 0.f, sb = 0.f;
+                            for (int w = 0; w < kw; ++w) {
+                                sa += red[w * kMegaMaxRows + lane];
+                                sb += red[w * kMegaMaxRows + rwc + lane];
+                            }
+                            if (kind == MOP_SWIGLU) {
+                                float val = sa;                       // native/mat_vec_kernel.cu:218-222
+                                val *= 1.0f / (1.0f + expf(-val));
+                                val *= sb;
+                                out0[ra] = __float2half_rn(val);
                             } else {
-                                o[ca.row0 + r] = __float2half_rn(sa);
-                                o[cb.row0 + r] = __float2half_rn(sb);
+                                __half* o = out_m;
+                                if (qm > 0) o += (long long)p.pos * p.kv_row_stride;
+                                if (qm < 2) {
+                                    // fp16 store of the mat-vec (native/mat_vec_kernel.cu:175), then RoPE on the rounded
+                                    // values (native/rope_kernel.cu:15-25)
+                                    const float a0 = __half2float(__float2half_rn(sa));
+                                    const float b0 = __half2float(__float2half_rn(sb));
+                                    o[ra] = __float2half_rn(a0 * cs.x - b0 * cs.y);
+                                    o[rb] = __float2half_rn(a0 * cs.y + b0 * cs.x);
+                                } else {
+                                    o[ra] = __float2half_rn(sa);
+                                    o[rb] = __float2half_rn(sb);
+                                }
+                            }
+                        }
+                    } else {
+                        const int row = tile * rows_per_tile + roff;
+                        const bool mine = lane < nrow && row < cols;
+                        const long long tw0 = now();
+                        wait_parked_or_abort(&done_bar[slot], par, &s_abort, p.status, 3u, k);
+                        tf_wait += now() - tw0;
+                        if (mine) {
+                            float sum = 0.f;
+                            for (int w = 0; w < kw; ++w) sum += red[w * kMegaMaxRows + roff];
+                            // the residual value was fetched by the consumers (they hold the operator's dependency) and
+                            // travels in the extra k-row of the partial slot
+                            if (kind == MOP_RESID)
+                                out0[row] = __float2half_rn(sum + red[kw * kMegaMaxRows + roff]);  // native/mat_vec_kernel.cu:154-156
+                            else if (kind == MOP_PARTIAL) {
+                                // row-sharded mat-vec: this rank's fp32 partial goes straight into every rank's receive
+                                // zone (plain peer stores over NVLink); the residual add and the single fp16 rounding
+                                // happen where the sum is consumed
+                                for (int q = 0; q < tp; ++q) gp->peer_out[q][row] = sum;
+                            } else if (tp > 1) {
+                                // vocabulary-sharded classifier: every rank ends up with the full logits
+                                const __half hv = __float2half_rn(sum);
+                                for (int q = 0; q < tp; ++q) gp->peer_logits[q][gp->out_row0 + row] = hv;
+                            } else {
+                                out0[row] = __float2half_rn(sum);
                             }
                         }
                     }
-                } else {
-                    const int nrow = op.nch * op.rwc;
-                    const int ch = lane / op.rwc, r = lane - ch * op.rwc;
-                    MegaChunk c{0, 0, 0};
-                    if (lane < nrow) c = mega_chunk(op, p.head_size, tile, ch);
-                    const bool mine = lane < nrow && r < c.nrows;
-                    const int row = c.row0 + r;
-                    wait_parked_or_abort(&done_bar[slot], (n / kMegaRedSlots) & 1u, &s_abort, p.status, 3u, k);
-                    if (mine) {
-                        float sum = 0.f;
-                        for (int w = 0; w < op.kw; ++w) sum += red[w * kMegaMaxRows + ch * op.rwc + r];
-                        // the residual value was fetched by the consumers (they hold the operator's dependency) and
-                        // travels in the extra k-row of the partial slot
-                        if (op.kind == MOP_RESID)
-                            op.out[0][row] = __float2half_rn(sum + red[op.kw * kMegaMaxRows + ch * op.rwc + r]);  // native/mat_vec_kernel.cu:154-156
-                        else if (op.kind == MOP_PARTIAL) {
-                            // row-sharded mat-vec: this rank's fp32 partial goes straight into every rank's receive
-                            // zone (plain peer stores over NVLink); the residual add and the single fp16 rounding
-                            // happen where the sum is consumed
-                            for (int q = 0; q < op.tp; ++q) op.peer_out[q][row] = sum;
-                        } else if (op.tp > 1) {
-                            // vocabulary-sharded classifier: every rank ends up with the full logits
-                            const __half hv = __float2half_rn(sum);
-                            for (int q = 0; q < op.tp; ++q) op.peer_logits[q][op.out_row0 + row] = hv;
-                        } else {
-                            op.out[0][row] = __float2half_rn(sum);
-                        }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&free_bar[slot]);
+                }
+                if (kind == MOP_QKV) {
+                    qpp += ncta;
+                    if (qpp >= ppm) {
+                        do { qpp -= ppm; ++qm; } while (qpp >= ppm);
+                        out_m = gp->out[qm < 2 ? qm : 2];
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&free_bar[slot]);
             }
             // this CTA's share of operator k is written: publish it. The warp barrier orders every lane's stores
             // before lane 0's release, which is cumulative at device scope.
             __syncwarp();
-            if ((op.kind == MOP_PARTIAL || op.kind == MOP_CLS) && op.tp > 1) {
+            if ((kind == MOP_PARTIAL || kind == MOP_CLS) && tp > 1) {
                 // published on every rank's counter: system-scope release after the peer stores of this warp
-                if (lane < op.tp) red_release_sys_add(op.peer_done[lane], 1u);
+                if (lane < tp) red_release_sys_add(gp->peer_done[lane], 1u);
             } else if (lane == 0) {
                 red_release_gpu_add(&p.done[k], 1u);
             }
+        }
+        if (kProf && p.prof && lane == 0) {
+            long long* o = p.prof + (size_t)cta * 64;
+            o[34 + 2 * fw] = now() - tf_all0;
+            o[35 + 2 * fw] = tf_wait;
         }
         return;
     }

@@ -594,7 +594,13 @@ static int build_mega(Model* m)
     }
     if (dim > 2 * 8 * kMegaConsumerWarps * 32) return ML2_OK;   // a normalised input vector is fetched as two pieces per thread
     const int att_bytes = (scratch + 127) & ~127;
-    const int budget = 200 * 1024;
+    // everything the opt-in limit of one CTA leaves after the kernel's static shared memory (1 KB kept spare)
+    int optin = 0;
+    ML2_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->ctx->device));
+    cudaFuncAttributes fa{};
+    ML2_CUDA(cudaFuncGetAttributes(&fa, decode_token_kernel<true>));
+    int budget = optin - (int)fa.sharedSizeBytes - 1024;
+    if (const char* e = getenv("ML2_MEGA_SMEM_KB")) budget = std::min(budget, atoi(e) * 1024);
     int nstage = (budget - att_bytes) / slot;
     if (nstage > kMegaMaxStages) nstage = kMegaMaxStages;
     if (nstage < 2) return ML2_OK;
