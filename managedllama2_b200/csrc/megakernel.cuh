@@ -523,9 +523,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         // ================= finalizers: fixed-order sum over k-warps + operator tail ========================
         const int fw = warp - kMegaConsumerWarps - 1;
         uint32_t n = 0;
-        long long tf_wait = 0, tf_all0 = now();
+        long long tf_wait = 0, tf_all0 = now(), tf_sum = 0, tf_store = 0, tf_rel = 0, tf_head = 0;
         for (int k = 0; k < p.nops; ++k) {
             // As in the producer, the operator's invariants sit in registers and nothing is divided per tile.
+            const long long th0 = now();
             const MegaOp* gp = p.ops + k;
             const int ntiles = gp->ntiles;
             if (ntiles == 0) continue;   // attention / argmax are published by the consumers
@@ -544,6 +545,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             __half* const out0 = gp->out[0];
             __half* out_m = kind == MOP_QKV ? gp->out[qm < 2 ? qm : 2] : out0;
             const int rows_per_tile = paired ? rwc : gp->nch * rwc;
+            tf_head += now() - th0 + (long long)(rows_per_tile + (int)(size_t)out_m) * 0;
             for (int i = 0; i < cnt; ++i, ++n) {
                 const bool take = (int)(n % kMegaFinalWarps) == fw;
                 if (take) {
@@ -569,12 +571,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         const long long tw0 = now();
                         wait_parked_or_abort(&done_bar[slot], par, &s_abort, p.status, 3u, k);
                         tf_wait += now() - tw0;
+                        float sa = 0.f, sb = 0.f;
                         if (mine) {
-                            float sa = 0.f, sb = 0.f;
                             for (int w = 0; w < kw; ++w) {
                                 sa += red[w * kMegaMaxRows + lane];
                                 sb += red[w * kMegaMaxRows + rwc + lane];
                             }
+                        }
+                        // the partial slot is read: hand it back BEFORE the global stores, so that the release of
+                        // this arrival does not have to wait for their acknowledgement
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&free_bar[slot]);
+                        if (mine) {
                             if (kind == MOP_SWIGLU) {
                                 float val = sa;                       // native/mat_vec_kernel.cu:218-222
                                 val *= 1.0f / (1.0f + expf(-val));
@@ -602,13 +610,21 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         const long long tw0 = now();
                         wait_parked_or_abort(&done_bar[slot], par, &s_abort, p.status, 3u, k);
                         tf_wait += now() - tw0;
+                        const long long ts0 = now();
+                        float sum = 0.f, res = 0.f;
                         if (mine) {
-                            float sum = 0.f;
                             for (int w = 0; w < kw; ++w) sum += red[w * kMegaMaxRows + roff];
                             // the residual value was fetched by the consumers (they hold the operator's dependency) and
                             // travels in the extra k-row of the partial slot
+                            if (kind == MOP_RESID) res = red[kw * kMegaMaxRows + roff];
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&free_bar[slot]);   // before the global stores (see above)
+                        const long long ts1 = now();
+                        tf_sum += ts1 - ts0;
+                        if (mine) {
                             if (kind == MOP_RESID)
-                                out0[row] = __float2half_rn(sum + red[kw * kMegaMaxRows + roff]);  // native/mat_vec_kernel.cu:154-156
+                                out0[row] = __float2half_rn(sum + res);  // native/mat_vec_kernel.cu:154-156
                             else if (kind == MOP_PARTIAL) {
                                 // row-sharded mat-vec: this rank's fp32 partial goes straight into every rank's receive
                                 // zone (plain peer stores over NVLink); the residual add and the single fp16 rounding
@@ -622,9 +638,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                                 out0[row] = __float2half_rn(sum);
                             }
                         }
+                        tf_store += now() - ts1;
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&free_bar[slot]);
+                    if (p.debug & 4) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&free_bar[slot]);
+                    }
                 }
                 if (kind == MOP_QKV) {
                     qpp += ncta;
@@ -636,6 +655,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             }
             // this CTA's share of operator k is written: publish it. The warp barrier orders every lane's stores
             // before lane 0's release, which is cumulative at device scope.
+            const long long tr0 = now();
             __syncwarp();
             if ((kind == MOP_PARTIAL || kind == MOP_CLS) && tp > 1) {
                 // published on every rank's counter: system-scope release after the peer stores of this warp
@@ -643,11 +663,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             } else if (lane == 0) {
                 red_release_gpu_add(&p.done[k], 1u);
             }
+            tf_rel += now() - tr0;
         }
         if (kProf && p.prof && lane == 0) {
             long long* o = p.prof + (size_t)cta * 64;
             o[34 + 2 * fw] = now() - tf_all0;
             o[35 + 2 * fw] = tf_wait;
+            if (fw == 0) { o[40] = tf_sum; o[41] = tf_store; o[42] = tf_rel; o[43] = tf_head; }
         }
         return;
     }
