@@ -222,6 +222,45 @@ int ml2_model_profile(ml2_model* model, int iters, double* avg_us6, double* algo
 /* Transformer.Generate on token ids (src/Transformer.cs:89-112): HOST buffers in and out, copies inside. */
 int ml2_model_generate(ml2_model* model, const int* prompt_host, int n_prompt, int steps, int* out_tokens_host, int* n_out);
 
+
+/* ---- model.bin reader -------------------------------------------------------------------------
+ * Stands for Config.LoadConfig (src/Config.cs:21-31) and the TransformerWeights constructor
+ * (src/TransformerWeights.cs:20-41, 54-103): the file written by src/ModelConverter.cs:130-177 is mapped
+ * read-only, the 32-byte header is checked (ropeTheta must be 10000), the tensor walk of the reference's reader
+ * is repeated (globals: embedding, classifier, final norm; per layer the QWeights query, key, value, output, up,
+ * gate, down as Weight / Zeros / Scales, then the two norm vectors) and the file must be consumed exactly.
+ * Host-only calls: ml2_model_file_open / _close / _config / _tensor need no GPU. */
+typedef struct ml2_model_file ml2_model_file;
+typedef struct ml2_weights ml2_weights;
+#define ML2_T_EMBED 0      /* global tensors: layer = -1, part = 0 */
+#define ML2_T_CLASSIFIER 1
+#define ML2_T_RMS_FINAL 2
+#define ML2_T_QUERY 0      /* layer tensors; QWeights have part 0 = Weight, 1 = Zeros, 2 = Scales */
+#define ML2_T_KEY 1
+#define ML2_T_VALUE 2
+#define ML2_T_OUTPUT 3
+#define ML2_T_UP 4
+#define ML2_T_GATE 5
+#define ML2_T_DOWN 6
+#define ML2_T_RMS_ATT 7
+#define ML2_T_RMS_FFN 8
+int ml2_model_file_open(const char* path, ml2_model_file** out);
+int ml2_model_file_close(ml2_model_file* file);
+int ml2_model_file_config(const ml2_model_file* file, ml2_config* out);
+/* Pointer into the mapping and byte length of one array of the file. */
+int ml2_model_file_tensor(const ml2_model_file* file, int layer, int tensor, int part, const void** data, uint64_t* bytes);
+/* Stands for the host-to-device copies of the Transformer constructor (src/Transformer.cs:58-61 and the
+ * CudaDeviceVariable assignments of src/TransformerWeights.cs): copies the shard that rank `tp_rank` of `tp_size`
+ * owns into one device allocation (outputs of query / key / value / gate / up and vocabulary rows by range, inputs
+ * of output / down as a window of whole groups of 128 with the zero points re-packed from the window's start). */
+int ml2_weights_upload(ml2_ctx* ctx, const ml2_model_file* file, int tp_size, int tp_rank, ml2_weights** out);
+/* ml2_model_bind_globals + ml2_model_bind_layer for every layer. The weights must outlive the model. */
+int ml2_weights_bind(const ml2_weights* weights, ml2_model* model);
+int ml2_weights_layer(const ml2_weights* weights, int layer, ml2_layer_weights* out);
+int ml2_weights_globals(const ml2_weights* weights, const void** embed, const void** classifier_local, const void** rms_final,
+                        uint64_t* device_bytes);
+int ml2_weights_free(ml2_weights* weights);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

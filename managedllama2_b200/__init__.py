@@ -11,10 +11,10 @@ from .modules import (Argmax, Config, CudaContext, Embedding, MatVec, MatVecResi
                       MatVecSwiGLU, QKVMatVec, QWeight, RMSNorm, RoPERotation, Softmax, VecMat, ceil_div,
                       qweight_sizes)
 
-from .transformer import (PerLayerWeight, Transformer, TransformerWeights, synthetic_weights,  # noqa: F401,E402
+from .transformer import (DeviceWeights, ModelFile, PerLayerWeight, Transformer, TransformerWeights, synthetic_weights,  # noqa: F401,E402
                           synthetic_weights_host, tp_shapes)
 
-__all__ = ["PerLayerWeight", "Transformer", "TransformerWeights", "synthetic_weights", "synthetic_weights_host", "tp_shapes",
+__all__ = ["DeviceWeights", "ModelFile", "PerLayerWeight", "Transformer", "TransformerWeights", "synthetic_weights", "synthetic_weights_host", "tp_shapes",
            "Argmax", "Config", "CudaContext", "Embedding", "MatVec", "MatVecResidual", "MatVecStrided",
            "MatVecSwiGLU", "QKVMatVec", "QWeight", "RMSNorm", "RoPERotation", "Softmax", "VecMat", "Ml2Error",
            "load", "declared_symbols", "ceil_div", "qweight_sizes", "LIB_PATH"]

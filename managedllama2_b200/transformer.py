@@ -156,8 +156,107 @@ def synthetic_weights_host(config, seed=31415, sigma=0.02):
     return out
 
 
+# tensor ids of ml2_model_file_tensor (include/ml2b200.h)
+T_EMBED, T_CLASSIFIER, T_RMS_FINAL = 0, 1, 2
+T_QUERY, T_KEY, T_VALUE, T_OUTPUT, T_UP, T_GATE, T_DOWN, T_RMS_ATT, T_RMS_FFN = range(9)
+
+
+class ModelFile:
+    """A ``model.bin`` of the reference (written by src/ModelConverter.cs:130-177), mapped read-only.
+
+    Stands for ``Config.LoadConfig`` (src/Config.cs:21-31) plus the tensor walk of the ``TransformerWeights``
+    constructor (src/TransformerWeights.cs:20-41): a wrong ``ropeTheta`` and a file that is not consumed exactly
+    raise, as they do there. Needs no GPU.
+    """
+
+    def __init__(self, path):
+        self.lib = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(self.lib.ml2_model_file_open(str(path).encode(), ctypes.byref(h)))
+        self.handle = h
+        cfg = _lib.ConfigStruct()
+        _lib.check(self.lib.ml2_model_file_config(h, ctypes.byref(cfg)))
+        self.config = Config(cfg.dim, cfg.hidden_dim, cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.vocab_size, cfg.seq_len,
+                             cfg.rope_theta)
+
+    def tensor(self, layer, tensor, part=0):
+        """numpy view (uint32 for Weight / Zeros, float16 otherwise) of one array of the file."""
+        data, nbytes = ctypes.c_void_p(), ctypes.c_uint64()
+        _lib.check(self.lib.ml2_model_file_tensor(self.handle, layer, tensor, part, ctypes.byref(data), ctypes.byref(nbytes)))
+        is_u32 = layer >= 0 and tensor <= T_DOWN and part < 2
+        buf = (ctypes.c_ubyte * nbytes.value).from_address(data.value)
+        return np.frombuffer(buf, dtype=np.uint32 if is_u32 else np.float16)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.ml2_model_file_close(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class DeviceWeights:
+    """This rank's shard of a ``ModelFile`` in device memory (one allocation owned by the library)."""
+
+    def __init__(self, ctx, model_file, tp_size=1, tp_rank=0):
+        self.lib = ctx._lib
+        h = ctypes.c_void_p()
+        _lib.check(self.lib.ml2_weights_upload(ctx.handle, model_file.handle, tp_size, tp_rank, ctypes.byref(h)))
+        self.handle = h
+        self.n_layers = model_file.config.numLayers
+
+    def layer(self, i):
+        s = _FileLayerStruct()
+        _lib.check(self.lib.ml2_weights_layer(self.handle, i, ctypes.byref(s)))
+        return s
+
+    def device_bytes(self):
+        n = ctypes.c_uint64()
+        _lib.check(self.lib.ml2_weights_globals(self.handle, None, None, None, ctypes.byref(n)))
+        return n.value
+
+    def globals(self):
+        e, c, r = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        _lib.check(self.lib.ml2_weights_globals(self.handle, ctypes.byref(e), ctypes.byref(c), ctypes.byref(r), None))
+        return e.value, c.value, r.value
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.ml2_weights_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class _FileLayerStruct(ctypes.Structure):
+    _fields_ = _LayerStruct._fields_
+
+
 class Transformer:
     """src/Transformer.cs on token ids. ``Forward`` is one CUDA-graph replay of the fused per-token sequence."""
+
+    @classmethod
+    def FromFile(cls, modelPath, cudaContext=None, tp_size=1, tp_rank=0, nccl_id=None):
+        """``new Transformer(modelPath, ...)`` (src/Transformer.cs:46-61): config and weights come from ``model.bin``."""
+        ctx = cudaContext or CudaContext(0)
+        with ModelFile(modelPath) as mf:
+            dw = DeviceWeights(ctx, mf, tp_size, tp_rank)
+            tr = cls(mf.config, dw, ctx, tp_size, tp_rank, nccl_id)
+        return tr
 
     def __init__(self, config: Config, weights: TransformerWeights, cudaContext: CudaContext = None, tp_size=1, tp_rank=0,
                  nccl_id: bytes = None):
@@ -174,6 +273,11 @@ class Transformer:
         idbuf = ctypes.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
         _lib.check(self.lib.ml2_model_create(self.ctx.handle, ctypes.byref(cfg), tp_size, tp_rank, idbuf, ctypes.byref(h)))
         self.handle = h
+        if isinstance(weights, DeviceWeights):
+            _lib.check(self.lib.ml2_weights_bind(weights.handle, h))
+            _lib.check(self.lib.ml2_model_alloc_runstate(h))
+            self.lib.ml2_model_launches_per_token.restype = ctypes.c_longlong
+            return
         _lib.check(self.lib.ml2_model_bind_globals(h, ctypes.c_void_p(weights.tokenEmbeddingTable.data_ptr()),
                                                    ctypes.c_void_p(weights.classifierWeights.data_ptr()),
                                                    ctypes.c_void_p(weights.rmsFinalWeight.data_ptr())))

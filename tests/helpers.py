@@ -45,3 +45,24 @@ def rel_err(got, want):
     rms = np.sqrt(np.mean(want * want)) if want.size else 0.0
     den = np.maximum(np.abs(want), max(rms, 1e-30))
     return float(np.max(np.abs(got - want) / den)) if want.size else 0.0
+
+
+def write_model_bin(path, cfg, hw):
+    """Writes a ``model.bin`` in the reference's layout (src/ModelConverter.cs:130-177; read back by
+    src/TransformerWeights.cs:33-41, 81-95): 32-byte Config header, embedding, classifier, final norm, then per layer
+    the QWeights query, key, value, output, UP, GATE, down (Weight, Zeros, Scales each) and the two norm vectors.
+    ``hw`` is the dict of ``synthetic_weights_host``."""
+    import struct
+    with open(path, "wb") as f:
+        f.write(struct.pack("<7if", cfg.dim, cfg.hiddenDim, cfg.numLayers, cfg.numHeads, cfg.numKVHeads, cfg.vocabSize,
+                            cfg.seqLength, cfg.ropeTheta))
+        for name in ("embed", "classifier", "rms_final"):
+            f.write(np.ascontiguousarray(hw[name], np.float16).tobytes())
+        for L in hw["layers"]:
+            for name in ("q", "k", "v", "o", "up", "gate", "down"):
+                w, z, s = L[name]
+                f.write(np.ascontiguousarray(w, np.uint32).tobytes())
+                f.write(np.ascontiguousarray(z, np.uint32).tobytes())
+                f.write(np.ascontiguousarray(s, np.float16).tobytes())
+            f.write(np.ascontiguousarray(L["rms_att"], np.float16).tobytes())
+            f.write(np.ascontiguousarray(L["rms_ffn"], np.float16).tobytes())

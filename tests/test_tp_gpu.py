@@ -19,3 +19,16 @@ def test_tensor_parallel_matches_oracle(world):
            "127.0.0.1", "--master-port", str(29600 + world), os.path.join(here, "tp_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "TP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_tensor_parallel_from_model_bin(tmp_path):
+    """Two ranks load their shards from one model.bin (the reference's file layout) and match the oracle."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "0"), ML2_TP_MODEL_BIN=str(tmp_path / "model.bin"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29611", os.path.join(here, "tp_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "TP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]

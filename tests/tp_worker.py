@@ -25,8 +25,18 @@ def main():
     # 8 heads, 13 hidden groups: uneven hidden split for 2, 4 and 8 ranks
     cfg = ml2.Config(dim=1024, hiddenDim=13 * 128, numLayers=2, numHeads=8, numKVHeads=8, vocabSize=512, seqLength=40)
     ctx = ml2.CudaContext(local)
-    w = ml2.synthetic_weights(ctx, cfg, seed=21, tp_size=world, tp_rank=rank)
-    tr = ml2.Transformer(cfg, w, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
+    model_bin = os.environ.get("ML2_TP_MODEL_BIN")
+    if model_bin:
+        # every rank cuts its shard out of one model.bin (rank 0 writes it in the reference's layout)
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from helpers import write_model_bin
+        if rank == 0:
+            write_model_bin(model_bin, cfg, ml2.synthetic_weights_host(cfg, seed=21))
+        dist.barrier()
+        tr = ml2.Transformer.FromFile(model_bin, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
+    else:
+        w = ml2.synthetic_weights(ctx, cfg, seed=21, tp_size=world, tp_rank=rank)
+        tr = ml2.Transformer(cfg, w, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
     if os.environ.get("ML2_TP_FUSED", "1") == "1":
         tr.attach_peers_with(dist)   # one persistent kernel per token, all-reduce over peer memory
     toks = [5, 99, 256, 31]
