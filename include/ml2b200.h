@@ -223,6 +223,25 @@ int ml2_model_profile(ml2_model* model, int iters, double* avg_us6, double* algo
 int ml2_model_generate(ml2_model* model, const int* prompt_host, int n_prompt, int steps, int* out_tokens_host, int* n_out);
 
 
+/* ---- sampling chain (Sampler.Sample, src/Sampler.cs:40-70) -----------------------------------
+ * One call per Module of the reference; every kernel is one CTA on the context's stream, in place.
+ * SoftmaxLogits.Forward (src/SoftmaxLogits.cs; native/softmax_logits_kernel.cu:10-60): indices[t] = t,
+ * logits := softmax(logits / temperature) with the reference's fp16 rounding points. */
+int ml2_softmax_logits(ml2_ctx* ctx, void* logits, int size, float temperature, int* indices);
+/* Sort.Forward (src/Sort.cs; native/sort_kernel.cu:13-45): fp16 keys descending, int values carried, equal keys
+ * keep their order. Any size from 1 to 32768 (the reference needs size = 125 * block size). */
+int ml2_sort(ml2_ctx* ctx, void* keys, int* values, int size);
+/* CumulativeSum.Forward (src/CumulativeSum.cs; native/cumulative_sum_kernel.cu:9-33): inclusive fp32 sum of fp16
+ * values, each output rounded to fp16. Any size (the reference needs size = 32 * block size). */
+int ml2_cumulative_sum(ml2_ctx* ctx, void* values, int size);
+/* SampleTopP.Forward (src/SampleTopP.cs; native/sample_top_p_kernel.cu:9-29): tokens[pos] = indices[first t with
+ * values[t] >= threshold], the last entry if none reaches it. */
+int ml2_sample_top_p(ml2_ctx* ctx, const void* values, const int* indices, int size, float threshold, int* tokens, int pos);
+/* Sampler.Sample for temperature != 0 (src/Sampler.cs:49-66) on the model's stream, after ml2_model_forward(...,
+ * write_token = 0): softmax, sort when 0 < top_p < 1 (threshold = coin * top_p, else coin), cumulative sum, pick;
+ * writes tokens[next_pos] and consumes the logits. `coin` is the host's uniform draw in [0,1). */
+int ml2_model_sample(ml2_model* model, int next_pos, float temperature, float top_p, float coin);
+
 /* ---- model.bin reader -------------------------------------------------------------------------
  * Stands for Config.LoadConfig (src/Config.cs:21-31) and the TransformerWeights constructor
  * (src/TransformerWeights.cs:20-41, 54-103): the file written by src/ModelConverter.cs:130-177 is mapped

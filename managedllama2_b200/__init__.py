@@ -9,6 +9,7 @@ PyTorch is used for device buffers and streams only.
 from ._lib import LIB_PATH, Ml2Error, declared_symbols, load  # noqa: F401
 from .modules import (Argmax, Config, CudaContext, Embedding, MatVec, MatVecResidual, MatVecStrided,  # noqa: F401
                       MatVecSwiGLU, QKVMatVec, QWeight, RMSNorm, RoPERotation, Softmax, VecMat, ceil_div,
+                      CumulativeSum, SampleTopP, SoftmaxLogits, Sort,
                       qweight_sizes)
 
 from .transformer import (DeviceWeights, ModelFile, PerLayerWeight, Transformer, TransformerWeights, synthetic_weights,  # noqa: F401,E402
@@ -16,5 +17,5 @@ from .transformer import (DeviceWeights, ModelFile, PerLayerWeight, Transformer,
 
 __all__ = ["DeviceWeights", "ModelFile", "PerLayerWeight", "Transformer", "TransformerWeights", "synthetic_weights", "synthetic_weights_host", "tp_shapes",
            "Argmax", "Config", "CudaContext", "Embedding", "MatVec", "MatVecResidual", "MatVecStrided",
-           "MatVecSwiGLU", "QKVMatVec", "QWeight", "RMSNorm", "RoPERotation", "Softmax", "VecMat", "Ml2Error",
+           "MatVecSwiGLU", "QKVMatVec", "CumulativeSum", "SampleTopP", "SoftmaxLogits", "Sort", "QWeight", "RMSNorm", "RoPERotation", "Softmax", "VecMat", "Ml2Error",
            "load", "declared_symbols", "ceil_div", "qweight_sizes", "LIB_PATH"]

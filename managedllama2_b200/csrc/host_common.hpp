@@ -37,4 +37,8 @@ int fail(int code, const char* fmt, ...);
 int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, MatVecPlan* pl);
 int launch_matvec(Ctx* ctx, Fmt fmt, Epi epi, Pro pro, const MatVecPlan& pl, MatVecParams prm, bool pdl);
 
+// sampling chain (sampler.cu): Sampler.Sample for temperature != 0 on `st`; the logits are consumed in place
+int sampler_chain(cudaStream_t st, int device, void* logits, int* indices, int size, float temperature, float top_p, float coin, int* tokens,
+                  int next_pos);
+
 }  // namespace ml2

@@ -180,6 +180,7 @@ struct Model {
     long long* mega_prof = nullptr;
     unsigned int* mega_done_ptr = nullptr;
     __half* logits_view = nullptr;          // where the full logits of the persistent kernel land
+    int* sample_indices = nullptr;          // token ids carried through the sampler's sort (RunState.indices)
     // tensor parallel persistent kernel: one peer-visible buffer per rank (counters, receive zones, logits)
     void* comm_local = nullptr;
     void* comm_peer[8] = {};
@@ -974,6 +975,25 @@ int ml2_model_read_token(ml2_model* h, int pos, int* token_host)
     ML2_CUDA(cudaMemcpyAsync(token_host, m->tokens + pos, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     return ML2_OK;
+}
+
+int ml2_model_sample(ml2_model* h, int next_pos, float temperature, float top_p, float coin)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "sample: null model");
+    if (next_pos < 0 || next_pos > m->cfg.seq_len) return fail(ML2_E_INVALID, "sample: next_pos=%d", next_pos);
+    if (!(temperature > 0.f)) return fail(ML2_E_INVALID, "sample: temperature %g (0 is the greedy path of ml2_model_forward)", (double)temperature);
+    if (m->cfg.vocab_size > 32768 && !(top_p <= 0.f || top_p >= 1.f))
+        return fail(ML2_E_INVALID, "sample: top-p sorting supports vocabularies up to 32768 (this one has %d)", m->cfg.vocab_size);
+    ML2_CUDA(cudaSetDevice(m->ctx->device));
+    if (!m->sample_indices) {
+        ML2_CUDA(cudaMalloc(&m->sample_indices, (size_t)m->cfg.vocab_size * sizeof(int)));   // RunState.indices (src/RunState.cs)
+        m->owned.push_back(m->sample_indices);
+    }
+    __half* lg = (m->mega_ok && m->logits_view) ? m->logits_view : m->logits;
+    const int rc = sampler_chain(m->stream, m->ctx->device, lg, m->sample_indices, m->cfg.vocab_size, temperature, top_p, coin, m->tokens, next_pos);
+    if (rc == ML2_OK) m->ctx->launches += (top_p <= 0.f || top_p >= 1.f) ? 3 : 4;
+    return rc;
 }
 
 int ml2_model_read_logits(ml2_model* h, void* logits_host_f16)

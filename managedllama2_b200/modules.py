@@ -227,3 +227,38 @@ class Argmax(Module):
     def Forward(self, logits, vocabSize, tokens, nextPos, generateToken):
         _lib.check(self.lib.ml2_argmax(self.ctx.handle, _ptr(logits), vocabSize, _ptr(tokens), nextPos,
                                        1 if generateToken else 0))
+
+
+class SoftmaxLogits(Module):
+    """src/SoftmaxLogits.cs:5-16."""
+
+    def Forward(self, logits, size, temperature, indices):
+        _lib.check(self.lib.ml2_softmax_logits(self.ctx.handle, _ptr(logits), size, ctypes.c_float(temperature), _ptr(indices)))
+
+
+class Sort(Module):
+    """src/Sort.cs:5-16 (descending by key, values carried; any size up to 32768)."""
+
+    def __init__(self, cudaContext, config=None):
+        super().__init__(cudaContext)
+
+    def Forward(self, logits, indices, size):
+        _lib.check(self.lib.ml2_sort(self.ctx.handle, _ptr(logits), _ptr(indices), size))
+
+
+class CumulativeSum(Module):
+    """src/CumulativeSum.cs:5-16."""
+
+    def __init__(self, cudaContext, config=None):
+        super().__init__(cudaContext)
+
+    def Forward(self, logits, size):
+        _lib.check(self.lib.ml2_cumulative_sum(self.ctx.handle, _ptr(logits), size))
+
+
+class SampleTopP(Module):
+    """src/SampleTopP.cs:5-16."""
+
+    def Forward(self, logits, indices, size, threshold, tokens, nextPos):
+        _lib.check(self.lib.ml2_sample_top_p(self.ctx.handle, _ptr(logits), _ptr(indices), size, ctypes.c_float(threshold),
+                                             _ptr(tokens), nextPos))

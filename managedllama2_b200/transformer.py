@@ -330,6 +330,32 @@ class Transformer:
                                                int(steps), out.ctypes.data_as(ctypes.c_void_p), ctypes.byref(n)))
         return out[:n.value].tolist()
 
+    def Sample(self, nextPosition, temperature, topP, coin):
+        """Sampler.Sample for temperature != 0 (src/Sampler.cs:49-66), after ``Forward(pos, next, False)``."""
+        _lib.check(self.lib.ml2_model_sample(self.handle, nextPosition, ctypes.c_float(temperature), ctypes.c_float(topP),
+                                             ctypes.c_float(coin)))
+
+    def GenerateSampled(self, promptTokens, steps, temperature=0.5, topP=0.9, seed=0):
+        """Transformer.Generate with the reference's default sampler settings (src/Transformer.cs:42, 89-112): prompt
+        tokens are forced, then one uniform draw per sampled token (``numpy`` generator instead of System.Random)."""
+        if temperature == 0.0:
+            return self.Generate(promptTokens, steps)
+        rng = np.random.default_rng(seed)
+        prompt = [int(t) for t in promptTokens]
+        self.set_tokens(np.array(prompt, np.int32))
+        out = []
+        for pos in range(steps):
+            self.Forward(pos, pos + 1, False)
+            if pos + 1 >= len(prompt):
+                self.Sample(pos + 1, temperature, topP, float(rng.random(dtype=np.float32)))
+                tok = self.read_token(pos + 1)
+            else:
+                tok = prompt[pos + 1]
+            if tok < 3:
+                break
+            out.append(tok)
+        return out
+
     # -- access to the run state -------------------------------------------------------------------
     def set_tokens(self, tokens, first=0):
         t = np.ascontiguousarray(tokens, dtype=np.int32)

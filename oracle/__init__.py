@@ -263,3 +263,45 @@ class CpuModel:
     def forward(self, token, pos):
         lib().orc_forward(ctypes.byref(self._m), ctypes.c_int(int(token)), ctypes.c_int(int(pos)))
         return self.logits.copy()
+
+
+# ---- sampling chain (numpy restatement of src/Sampler.cs:40-70 and its four kernels) --------------------------
+
+def softmax_logits(logits, temperature):
+    """native/softmax_logits_kernel.cu:10-54: returns (probabilities fp16, indices). fp16 rounding after the division
+    by the temperature, of every exponential (the sum uses the unrounded ones) and of the final quotient."""
+    x = (_f16(logits).astype(np.float32) / np.float32(temperature)).astype(np.float16)
+    mx = x.astype(np.float32).max()
+    v = np.exp(x.astype(np.float32) - mx, dtype=np.float32)
+    total = np.float32(v.sum(dtype=np.float32))
+    probs = (v.astype(np.float16).astype(np.float32) / total).astype(np.float16)
+    return probs, np.arange(x.size, dtype=np.int32)
+
+
+def sort_desc(keys, values):
+    """native/sort_kernel.cu:13-45: keys descending, values carried, ties in their original order (stable radix sort)."""
+    keys = _f16(keys)
+    order = np.argsort(-keys.astype(np.float32), kind="stable")
+    return keys[order], np.asarray(values, np.int32)[order]
+
+
+def cumulative_sum(values):
+    """native/cumulative_sum_kernel.cu:9-28 / test/CumulativeSumTests.cs:44-56: running fp32 sum, each rounded to fp16."""
+    with np.errstate(over="ignore"):   # sums beyond the fp16 range become infinities, as the kernel's cast makes them
+        return np.cumsum(_f16(values).astype(np.float32), dtype=np.float32).astype(np.float16)
+
+
+def sample_top_p(values, indices, threshold):
+    """native/sample_top_p_kernel.cu:9-24: indices[first t with values[t] >= threshold], the last entry if none."""
+    hit = np.nonzero(_f16(values).astype(np.float32) >= np.float32(threshold))[0]
+    return int(np.asarray(indices)[hit[0] if hit.size else len(values) - 1])
+
+
+def sample(logits, temperature, top_p, coin):
+    """Sampler.Sample for temperature != 0 (src/Sampler.cs:49-66)."""
+    probs, idx = softmax_logits(logits, temperature)
+    threshold = np.float32(coin)
+    if 0.0 < top_p < 1.0:
+        probs, idx = sort_desc(probs, idx)
+        threshold = np.float32(coin) * np.float32(top_p)
+    return sample_top_p(cumulative_sum(probs), idx, threshold)

@@ -21,6 +21,10 @@ KERNELS = {
     "rope_kernel": ["rope_kernel"],
     "embedding_kernel": ["embedding_kernel"],
     "argmax_kernel": ["argmax_kernel"],
+    "softmax_logits_kernel": ["softmax_logits_kernel"],
+    "sort_kernel": ["sort_kernel"],
+    "cumulative_sum_kernel": ["cumulative_sum_kernel"],
+    "sample_top_p_kernel": ["sample_top_p_kernel"],
 }
 
 
@@ -128,6 +132,21 @@ class RefModules:
 
     def argmax(self, logits, vocab, tokens, next_pos, write):          # src/Argmax.cs:10-15
         self.k.launch("argmax_kernel", (1,), (1024,), (logits, vocab, tokens, next_pos, bool(write)), (P, I, P, I, B))
+
+    # the sampling chain (src/Sampler.cs:49-66) with the launch shapes of its Module classes
+    def softmax_logits(self, logits, size, temperature, indices):     # src/SoftmaxLogits.cs:9-15
+        self.k.launch("softmax_logits_kernel", (1,), (1024,), (logits, size, temperature, indices), (P, I, F, P))
+
+    def sort(self, keys, values, size):                                # src/Sort.cs:9-15: size must be 125 * block
+        assert size % 125 == 0 and size // 125 <= 1024
+        self.k.launch("sort_kernel", (1,), (size // 125,), (keys, values, size), (P, P, I))
+
+    def cumulative_sum(self, values, size):                            # src/CumulativeSum.cs:9-15: size must be 32 * block
+        assert size % 32 == 0 and size // 32 <= 1024
+        self.k.launch("cumulative_sum_kernel", (1,), (size // 32,), (values, size), (P, I))
+
+    def sample_top_p(self, values, indices, size, threshold, tokens, pos):   # src/SampleTopP.cs:9-15
+        self.k.launch("sample_top_p_kernel", (1,), (1024,), (values, indices, size, threshold, tokens, pos), (P, P, I, F, P, I))
 
 
 class RefTransformer:
