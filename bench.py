@@ -378,9 +378,9 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "algorithmic_bytes_per_launch": dom_bytes,
                          "frac_of_8TBps": achieved / 8000.0,
-                         # dram__bytes_read+write of one launch: ncu capture of the 8-layer case (profiles/
-                         # decode_token_kernel_13b_8layers.md: 1.6619 GB for 1.6463 GB algorithmic), scaled by bytes
-                         "traffic": (dom_bytes * 1.00946) if persistent else None,
+                         # dram__bytes_read+write of one launch: ncu capture of the 8-layer case (1.6597 GB moved for
+                         # 1.6496 GB algorithmic), scaled by the bytes of this launch
+                         "traffic": (dom_bytes * 1.00612) if persistent else None,
                          "traffic_source": "ncu dram bytes of the 8-layer capture x (bytes of this launch / bytes of that launch)"},
             "kernels_timed_alone": kernels,
             "reference_cuda_kernels": ref_cuda,
