@@ -151,10 +151,13 @@ __device__ __forceinline__ void word_dot(uint32_t w, const uint32_t* xp, float& 
 
 __device__ __forceinline__ float half_bits_to_float(unsigned short h) { return __half2float(__ushort_as_half(h)); }
 
-// Builds the stationary input slice of a lane from its 32 inputs in natural order (16 fp16 pairs).
+// Builds the stationary input slice of a lane from its 32 inputs in natural order (16 fp16 pairs). The sums come
+// from mixed-precision FMAs against the constant -1024 (fp16 in, fp32 accumulate): no fp16 -> fp32 conversions,
+// which issue at a fraction of the FMA rate.
 __device__ __forceinline__ void make_xslice(const uint32_t (&xr)[16], XSlice& xs)
 {
-    float s02 = 0.f, sodd = 0.f, s46 = 0.f;
+    constexpr unsigned short kM1024 = 0xE400;   // fp16 -1024
+    float e0 = 0.f, e1 = 0.f, o0 = 0.f, o1 = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint32_t h01 = xr[4 * j], h23 = xr[4 * j + 1], h45 = xr[4 * j + 2], h67 = xr[4 * j + 3];
@@ -162,17 +165,18 @@ __device__ __forceinline__ void make_xslice(const uint32_t (&xr)[16], XSlice& xs
         xs.xp[4 * j + 1] = __byte_perm(h01, h45, 0x7632);   // (x1, x5)
         xs.xp[4 * j + 2] = __byte_perm(h23, h67, 0x5410);   // (x2, x6)
         xs.xp[4 * j + 3] = __byte_perm(h23, h67, 0x7632);   // (x3, x7)
-        const float x0 = __half2float(__ushort_as_half(lo16(h01))), x1 = __half2float(__ushort_as_half(hi16(h01)));
-        const float x2 = __half2float(__ushort_as_half(lo16(h23))), x3 = __half2float(__ushort_as_half(hi16(h23)));
-        const float x4 = __half2float(__ushort_as_half(lo16(h45))), x5 = __half2float(__ushort_as_half(hi16(h45)));
-        const float x6 = __half2float(__ushort_as_half(lo16(h67))), x7 = __half2float(__ushort_as_half(hi16(h67)));
-        s02 += x0 + x2;
-        sodd += (x1 + x3) + (x5 + x7);
-        s46 += x4 + x6;
+        e0 = fma_f16_f32(lo16(h01), kM1024, e0);
+        o0 = fma_f16_f32(hi16(h01), kM1024, o0);
+        e1 = fma_f16_f32(lo16(h23), kM1024, e1);
+        o1 = fma_f16_f32(hi16(h23), kM1024, o1);
+        e0 = fma_f16_f32(lo16(h45), kM1024, e0);
+        o0 = fma_f16_f32(hi16(h45), kM1024, o0);
+        e1 = fma_f16_f32(lo16(h67), kM1024, e1);
+        o1 = fma_f16_f32(hi16(h67), kM1024, o1);
     }
-    xs.a0 = -1024.0f * (s02 + s46);
-    xs.b0 = -1024.0f * sodd;
-    xs.c1 = s02 + sodd + s46;
+    xs.a0 = e0 + e1;                                   // -1024 * S(even inputs)
+    xs.b0 = o0 + o1;                                   // -1024 * S(odd inputs)
+    xs.c1 = (xs.a0 + xs.b0) * -0.0009765625f;          // S(all inputs): the scaling by 1/1024 is exact
 }
 
 // Loads the lane's input slice (NX halves starting at element e0), optionally applying RMSNorm
