@@ -876,9 +876,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         const uint32_t w4[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float a0 = half_bits_to_float(lo16(w4[e])), a1 = half_bits_to_float(hi16(w4[e]));
-                            ss = fmaf(a0, a0, ss);
-                            ss = fmaf(a1, a1, ss);
+                            // fp16 x fp16 is exact in fp32: the mixed FMA gives fmaf(float(x), float(x), ss) bit for bit
+                            ss = fma_f16_f32(lo16(w4[e]), lo16(w4[e]), ss);
+                            ss = fma_f16_f32(hi16(w4[e]), hi16(w4[e]), ss);
                         }
                     }
                 }
