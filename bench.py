@@ -215,7 +215,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         dist.broadcast(idt, 0)
         nccl_id = bytes(idt.cpu().numpy().tobytes())
 
-    seq_len = PROMPT_LEN + args.warmup + 2 * args.steps + 8
+    seq_len = max(PROMPT_LEN, args.context) + args.warmup + 2 * args.steps + 8
     config = ml2.Config(seqLength=seq_len, **cfg)
     ctx = ml2.CudaContext(local_rank)
     weights = ml2.synthetic_weights(ctx, config, seed=SEED, tp_size=world, tp_rank=rank)
@@ -240,6 +240,10 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     for _ in range(PROMPT_LEN - 1):
         tr.Forward(pos, pos + 1, False)
         pos += 1
+    if args.context > pos:
+        # long-context timing aid (BASELINE configs[4]): continue from position `context`; the cache rows in between hold
+        # whatever the allocation held, the attention still reads and weighs all of them
+        pos = args.context
     for _ in range(args.warmup):
         tr.Forward(pos, pos + 1, True)
         pos += 1
@@ -368,7 +372,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
             "config": {"workload": "llama2-%s-shape%s AWQ int4 g128, batch-1 greedy decode, %d-token prompt then decode" %
-                                   (args.config, (" cut to %d layers" % args.layers) if args.layers else "", PROMPT_LEN),
+                                   (args.config, (" cut to %d layers" % args.layers) if args.layers else "", PROMPT_LEN) +
+                                   ((" from position %d" % args.context) if args.context else ""),
                        "parallelism": "tp%d" % world, "l2": "per-token working set %.2f GB per GPU, far larger than L2" % (tb / 1e9),
                        "bytes_per_token_per_gpu": tb},
             "hbm_frac_of_token": {"achieved_GB/s": tb * tokens_per_s / 1e9, "of_%s_peak" % peak_kind: tb * tokens_per_s / 1e9 / peak,
@@ -404,6 +409,7 @@ def main():
     ap.add_argument("--config", default="13b", choices=sorted(CONFIGS))
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the shape with fewer layers (smaller device footprint)")
     ap.add_argument("--no-cpu", action="store_true", help="profiling aid: skip the CPU baseline leg")
+    ap.add_argument("--context", type=int, default=0, help="profiling aid: time the decode steps from this position on (long-context case)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

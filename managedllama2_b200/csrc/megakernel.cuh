@@ -62,6 +62,12 @@ struct MegaOp {
     float* peer_out[8];      // MOP_PARTIAL: this rank's row block inside every rank's receive zone
     __half* peer_logits[8];  // sharded MOP_CLS: every rank's full logits buffer
     unsigned int* peer_done[8];  // this operator's counter on every rank
+    // attention split over several CTAs per head (long contexts):
+    float* att_ml;           // [heads][split][2]: running maximum and exp-sum of every part
+    float* att_part;         // [heads][split][head_size]: fp32 partial outputs (MOP_ATTN writes, the next operator sums them)
+    unsigned int* att_cnt;   // [heads]: arrivals of the parts, monotonically increasing
+    int att_layer;           // layer index (the counters advance once per layer and token)
+    int pad2;
 };
 
 struct MegaParams {
@@ -79,6 +85,9 @@ struct MegaParams {
     int dim, head_size, heads_local, kv_row_stride, vocab;
     float eps, scale;
     int nstage, slot_bytes, att_cap;
+    int att_split;             // CTAs per head for this token's attention (1: one CTA per head)
+    unsigned int att_seq;      // 1, 2, 3, ... over the tokens that used the split path
+    int n_layers;
     int debug;                 // bit 0: consumers skip the arithmetic (pipeline probe)
     long long* prof;           // optional [gridDim.x][64] cycle counters (diagnostics), may be null
 };
@@ -91,6 +100,8 @@ constexpr int kMegaMaxStages = 12;
 constexpr int kMegaRedSlots = 8;
 constexpr int kMegaMaxRows = 8;       // rows per tile
 constexpr int kMegaMaxGroups = 5;
+constexpr int kMegaMaxSplit = 8;     // CTAs per head of the split attention
+constexpr int kAttUnroll = 4;        // cache rows a warp keeps in flight
 constexpr uint32_t kBarCount = 64;    // fixed arrival count of the consumer-side mbarriers (see arrive_n)
 
 __device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n)
@@ -705,27 +716,49 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
 
         if (op.kind == MOP_ATTN) {
             wait_dependency();
-            // ---- attention of head `cta` (reference: mat_vec_strided / softmax / vec_mat kernels) -------------
-            if (cta < p.heads_local) {
+            // ---- attention (reference: mat_vec_strided / softmax / vec_mat kernels): `att_split` CTAs per head, each
+            // over a contiguous part of the sequence (1 for short contexts, more when the cache rows are many) ----
+            // Every part computes its scores (rounded to fp16 like native/mat_vec_kernel.cu:72-73), their maximum m_p and
+            // exp-sum l_p; the parts of a head exchange (m_p, l_p) through global memory; the probabilities are rounded
+            // to fp16 after the division by the GLOBAL sum (native/softmax_kernel.cu:46); the fp32 partial outputs are
+            // summed by the operator that consumes them (single fp16 rounding, native/vec_mat_kernel.cu:41).
+            const int S = p.att_split > 1 ? p.att_split : 1;
+            if (cta < p.heads_local * S) {
                 float* s_sc = reinterpret_cast<float*>(smem_raw + (size_t)p.nstage * p.slot_bytes);
-                const int head = cta;
+                const int head = cta / S, part = cta - head * S;
                 const int nseq = p.pos + 1;
-                const __half* kh = op.kcache + (size_t)head * p.head_size;
-                const __half* vh = op.vcache + (size_t)head * p.head_size;
+                const int chunk = (nseq + S - 1) / S;
+                const int t0 = part * chunk;
+                const int t1 = min(nseq, t0 + chunk);
+                const size_t stride = (size_t)p.kv_row_stride;
+                const __half* kh = op.kcache + (size_t)head * p.head_size + lane * 4;
+                const __half* vh = op.vcache + (size_t)head * p.head_size + lane * 4;
                 const uint2 qv = *reinterpret_cast<const uint2*>(op.in + (size_t)head * p.head_size + lane * 4);
                 float mx = -INFINITY;
-                for (int t = warp; t < nseq; t += kMegaConsumerWarps) {
-                    const uint2 kv = *reinterpret_cast<const uint2*>(kh + (size_t)t * p.kv_row_stride + lane * 4);
-                    float s = 0.f;
-                    s = fma_f16_f32(lo16(kv.x), lo16(qv.x), s);
-                    s = fma_f16_f32(hi16(kv.x), hi16(qv.x), s);
-                    s = fma_f16_f32(lo16(kv.y), lo16(qv.y), s);
-                    s = fma_f16_f32(hi16(kv.y), hi16(qv.y), s);
-                    s = warp_sum(s);
-                    const float sr = __half2float(__float2half_rn(s * p.scale));   // native/mat_vec_kernel.cu:72-73
-                    if (lane == 0) s_sc[t] = sr;
-                    mx = fmaxf(mx, sr);
+                for (int b = t0 + warp * kAttUnroll; b < t1; b += kMegaConsumerWarps * kAttUnroll) {
+                    uint2 kv[kAttUnroll];
+#pragma unroll
+                    for (int u = 0; u < kAttUnroll; ++u)
+                        kv[u] = (b + u < t1) ? *reinterpret_cast<const uint2*>(kh + (size_t)(b + u) * stride) : make_uint2(0u, 0u);
+                    float sc[kAttUnroll];
+#pragma unroll
+                    for (int u = 0; u < kAttUnroll; ++u) {
+                        float a = 0.f;
+                        a = fma_f16_f32(lo16(kv[u].x), lo16(qv.x), a);
+                        a = fma_f16_f32(hi16(kv[u].x), hi16(qv.x), a);
+                        a = fma_f16_f32(lo16(kv[u].y), lo16(qv.y), a);
+                        a = fma_f16_f32(hi16(kv[u].y), hi16(qv.y), a);
+                        sc[u] = a;
+                    }
+                    transpose_reduce<kAttUnroll>(sc, lane);   // lane 4 * u holds row u
+                    const int u = lane >> 2;
+                    if ((lane & 3) == 0 && b + u < t1) {
+                        const float sr = __half2float(__float2half_rn(sc[0] * p.scale));
+                        s_sc[b + u - t0] = sr;
+                        mx = fmaxf(mx, sr);
+                    }
                 }
+                mx = warp_max(mx);
                 if (lane == 0) s_att_tmp[warp] = mx;
                 named_bar_sync(1, kConsThreads);
                 mx = s_att_tmp[0];
@@ -733,34 +766,65 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 for (int w = 1; w < kMegaConsumerWarps; ++w) mx = fmaxf(mx, s_att_tmp[w]);
                 named_bar_sync(1, kConsThreads);
                 float sum = 0.f;
-                for (int i = tid; i < nseq; i += kConsThreads) {
-                    const float e = expf(s_sc[i] - mx);                          // native/softmax_kernel.cu:37
+                for (int i = tid; i < t1 - t0; i += kConsThreads) {
+                    const float e = expf(s_sc[i] - mx);
                     s_sc[i] = e;
                     sum += e;
                 }
                 sum = warp_sum(sum);
                 if (lane == 0) s_att_tmp[warp] = sum;
                 named_bar_sync(1, kConsThreads);
-                float total = 0.f;
+                float lsum = 0.f;
 #pragma unroll
-                for (int w = 0; w < kMegaConsumerWarps; ++w) total += s_att_tmp[w];
+                for (int w = 0; w < kMegaConsumerWarps; ++w) lsum += s_att_tmp[w];
+                // exchange with the other parts of this head
+                float* ml = op.att_ml + (size_t)head * S * 2;
+                float gm = mx, total = lsum, fac = 1.0f;
+                if (S > 1) {
+                if (tid == 0) {
+                    ml[part * 2] = mx;
+                    ml[part * 2 + 1] = lsum;
+                    __threadfence();
+                    red_release_gpu_add(&op.att_cnt[head], 1u);
+                    const unsigned int want = ((p.att_seq - 1u) * (unsigned int)p.n_layers + (unsigned int)op.att_layer + 1u) * (unsigned int)S;
+                    mega_wait_counter(&op.att_cnt[head], want, &s_abort, p.status, 6u, k, false);
+                }
+                named_bar_sync(1, kConsThreads);
+                gm = -INFINITY;
+                for (int q = 0; q < S; ++q) gm = fmaxf(gm, __ldcg(&ml[q * 2]));
+                total = 0.f;
+                for (int q = 0; q < S; ++q) {
+                    const float lq = __ldcg(&ml[q * 2 + 1]);
+                    if (lq > 0.f) total += lq * expf(__ldcg(&ml[q * 2]) - gm);
+                }
+                fac = (t1 > t0) ? expf(mx - gm) : 0.f;
+                }
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int t = warp; t < nseq; t += kMegaConsumerWarps) {
-                    const unsigned short pr = __half_as_ushort(__float2half_rn(s_sc[t] / total));   // native/softmax_kernel.cu:46
-                    const uint2 vv = *reinterpret_cast<const uint2*>(vh + (size_t)t * p.kv_row_stride + lane * 4);
-                    acc[0] = fma_f16_f32(pr, lo16(vv.x), acc[0]);
-                    acc[1] = fma_f16_f32(pr, hi16(vv.x), acc[1]);
-                    acc[2] = fma_f16_f32(pr, lo16(vv.y), acc[2]);
-                    acc[3] = fma_f16_f32(pr, hi16(vv.y), acc[3]);
+                for (int b = t0 + warp * kAttUnroll; b < t1; b += kMegaConsumerWarps * kAttUnroll) {
+                    uint2 vv[kAttUnroll];
+#pragma unroll
+                    for (int u = 0; u < kAttUnroll; ++u)
+                        vv[u] = (b + u < t1) ? *reinterpret_cast<const uint2*>(vh + (size_t)(b + u) * stride) : make_uint2(0u, 0u);
+#pragma unroll
+                    for (int u = 0; u < kAttUnroll; ++u) {
+                        if (b + u < t1) {
+                            const unsigned short pr = __half_as_ushort(__float2half_rn(s_sc[b + u - t0] * fac / total));
+                            acc[0] = fma_f16_f32(pr, lo16(vv[u].x), acc[0]);
+                            acc[1] = fma_f16_f32(pr, hi16(vv[u].x), acc[1]);
+                            acc[2] = fma_f16_f32(pr, lo16(vv[u].y), acc[2]);
+                            acc[3] = fma_f16_f32(pr, hi16(vv[u].y), acc[3]);
+                        }
+                    }
                 }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s_att_acc[warp][lane * 4 + e] = acc[e];
                 named_bar_sync(1, kConsThreads);
                 if (tid < p.head_size) {
-                    float s = 0.f;
+                    float o = 0.f;
 #pragma unroll
-                    for (int w = 0; w < kMegaConsumerWarps; ++w) s += s_att_acc[w][tid];
-                    op.out[0][(size_t)head * p.head_size + tid] = __float2half_rn(s);   // native/vec_mat_kernel.cu:41
+                    for (int w = 0; w < kMegaConsumerWarps; ++w) o += s_att_acc[w][tid];
+                    if (S > 1) op.att_part[((size_t)head * S + part) * p.head_size + tid] = o;
+                    else op.out[0][(size_t)head * p.head_size + tid] = __float2half_rn(o);   // native/vec_mat_kernel.cu:41
                 }
                 __threadfence();
                 named_bar_sync(1, kConsThreads);
@@ -840,7 +904,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         {
             const __half* src = op.in;
             if (op.pro == 2) src = p.embed + (size_t)p.tokens[p.pos] * op.rows;   // native/embedding_kernel.cu:6-12
-            if (op.pro == 0) {
+            if (op.pro == 0 && op.att_part != nullptr && p.att_split > 1) {
+                // input = attention output of the split path: fp32 partials of the parts, summed in part order and
+                // rounded to fp16 once (native/vec_mat_kernel.cu:41)
+                const int S = p.att_split;
+                for (int i = tid; i < nvec8; i += kConsThreads) {
+                    const int e = i * 8, head = e / p.head_size, d = e - head * p.head_size;
+                    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int q = 0; q < S; ++q) {
+                        const float4* pp = reinterpret_cast<const float4*>(op.att_part + ((size_t)head * S + q) * p.head_size + d);
+                        const float4 p0 = __ldcg(pp), p1 = __ldcg(pp + 1);
+                        a[0] += p0.x; a[1] += p0.y; a[2] += p0.z; a[3] += p0.w;
+                        a[4] += p1.x; a[5] += p1.y; a[6] += p1.z; a[7] += p1.w;
+                    }
+                    uint32_t o4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        o4[j] = (uint32_t)__half_as_ushort(__float2half_rn(a[2 * j])) | ((uint32_t)__half_as_ushort(__float2half_rn(a[2 * j + 1])) << 16);
+                    *reinterpret_cast<uint4*>(s_vec + (size_t)i * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+                }
+            } else if (op.pro == 0) {
                 for (int i = tid; i < nvec8; i += kConsThreads)
                     *reinterpret_cast<uint4*>(s_vec + (size_t)i * 8) = *reinterpret_cast<const uint4*>(src + (size_t)i * 8);
             } else {

@@ -181,6 +181,13 @@ struct Model {
     unsigned int* mega_done_ptr = nullptr;
     __half* logits_view = nullptr;          // where the full logits of the persistent kernel land
     int* sample_indices = nullptr;          // token ids carried through the sampler's sort (RunState.indices)
+    // attention split over several CTAs per head (persistent kernel, long contexts)
+    float* att_ml = nullptr;
+    float* att_part = nullptr;
+    unsigned int* att_cnt = nullptr;
+    int att_split = 1;                      // CTAs per head when the split path is taken (1: never)
+    int att_min_seq = 384;                  // shortest sequence that takes it
+    unsigned int att_seq = 0;
     // tensor parallel persistent kernel: one peer-visible buffer per rank (counters, receive zones, logits)
     void* comm_local = nullptr;
     void* comm_peer[8] = {};
@@ -490,6 +497,19 @@ static int build_mega(Model* m)
     std::vector<MegaOp> ops;
     const size_t kv_layer = (size_t)c.seq_len * m->dim_local;
     long long tiles_before = 0;
+    // split attention: scratch for the exchange between the parts of a head, and the counters of their arrivals
+    bool split_ok = !getenv("ML2_NO_ATT_SPLIT");
+    const int split = std::min(kMegaMaxSplit, m->ctx->sm_count / std::max(1, m->heads_local));
+    if (!m->att_ml) {
+        ML2_CUDA(cudaMalloc(&m->att_ml, (size_t)m->heads_local * kMegaMaxSplit * 2 * sizeof(float)));
+        ML2_CUDA(cudaMalloc(&m->att_part, (size_t)m->heads_local * kMegaMaxSplit * hs * sizeof(float)));
+        ML2_CUDA(cudaMalloc(&m->att_cnt, (size_t)m->heads_local * sizeof(unsigned int)));
+        m->owned.push_back(m->att_ml);
+        m->owned.push_back(m->att_part);
+        m->owned.push_back(m->att_cnt);
+    }
+    ML2_CUDA(cudaMemsetAsync(m->att_cnt, 0, (size_t)m->heads_local * sizeof(unsigned int), m->stream));
+    m->att_seq = 0;
     auto push = [&](MegaOp& op) {
         op.rot = (int)(tiles_before % m->ctx->sm_count);
         tiles_before += op.ntiles;
@@ -536,12 +556,15 @@ static int build_mega(Model* m)
         push(q);
         MegaOp a{};
         a.kind = MOP_ATTN; a.tp = 1; a.in = m->q; a.out[0] = m->xb; a.kcache = kc; a.vcache = vc; a.ntiles = 0;
+        a.att_ml = m->att_ml; a.att_part = m->att_part; a.att_cnt = m->att_cnt; a.att_layer = l;
         push(a);
         MegaOp o{};
         o.kind = MOP_RESID; o.pro = 0; o.nmat = 1;
         if (!mega_plan_op(o, 0, m->dim_local, dim, false, true)) return ML2_OK;
         o.ntiles = ceil_div(dim, o.run_rows);
         o.mat[0] = qwp(L.o); o.out[0] = x_cur; o.in = m->xb;
+        if (o.passes > 1) split_ok = false;   // the multi-sweep prologue reads its input vector as stored
+        o.att_part = m->att_part;
         if (tp) partial_output(o, (int)ops.size());
         push(o);
         MegaOp g{};
@@ -582,6 +605,8 @@ static int build_mega(Model* m)
     am.kind = MOP_ARGMAX; am.ntiles = 0; am.tp = 1;
     push(am);
 
+    m->att_split = (split_ok && split >= 2) ? split : 1;
+    if (const char* e = getenv("ML2_ATT_MIN_SEQ")) m->att_min_seq = atoi(e);
     int slot = 0;
     for (const MegaOp& op : ops)
         if (op.ntiles > 0) slot = std::max(slot, op.nruns * op.chunk_bytes);
@@ -655,6 +680,9 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     prm.eps = m->eps; prm.scale = 1.0f / sqrtf((float)m->head_size);
     prm.nstage = m->mega_nstage; prm.slot_bytes = m->mega_slot; prm.att_cap = m->cfg.seq_len;
     prm.prof = m->mega_prof;
+    prm.n_layers = m->cfg.n_layers;
+    prm.att_split = (m->att_split > 1 && pos + 1 >= m->att_min_seq) ? m->att_split : 1;
+    prm.att_seq = prm.att_split > 1 ? ++m->att_seq : m->att_seq;
     { const char* d = getenv("ML2_MEGA_DEBUG"); prm.debug = d ? atoi(d) : 0; }
     void* args[] = {&prm};
     const void* fn = m->mega_prof ? (const void*)decode_token_kernel<true> : (const void*)decode_token_kernel<false>;

@@ -131,3 +131,27 @@ def test_long_sequence_cluster_path():
             assert np.abs(got - want).max() <= 2e-2 * want.std(), pos
     tr.close()
     ctx.close()
+
+
+@pytest.mark.parametrize("heads", [2, 5])
+def test_split_attention_in_the_persistent_kernel(monkeypatch, heads):
+    """Several CTAs per head (the long-context path of the persistent kernel), forced on from the second position so
+    that parts without any cache row, one-row parts and uneven parts all occur; logits against the oracle."""
+    import managedllama2_b200 as ml2
+    monkeypatch.setenv("ML2_ATT_MIN_SEQ", "2")
+    cfg = ml2.Config(dim=128 * heads, hiddenDim=384, numLayers=2, numHeads=heads, numKVHeads=heads, vocabSize=256, seqLength=300)
+    ctx = ml2.CudaContext(0)
+    tr = ml2.Transformer(cfg, ml2.synthetic_weights(ctx, cfg, seed=6), ctx)
+    cpu, _ = oracle_model(ml2, cfg, 6)
+    rng = np.random.default_rng(3)
+    toks = rng.integers(3, cfg.vocabSize, size=cfg.seqLength).astype(np.int32)
+    tr.set_tokens(toks)
+    for pos in range(cfg.seqLength - 1):
+        tr.Forward(pos, pos + 1, False)
+        want = cpu.forward(toks[pos], pos).astype(np.float32)
+        if pos < 20 or pos in (31, 32, 63, 64, 100, 167, 255, 298):
+            got = tr.logits().astype(np.float32)
+            assert np.abs(got - want).max() <= 2e-2 * want.std(), pos
+    assert ctx.status() == (0, 0)
+    tr.close()
+    ctx.close()
