@@ -242,6 +242,16 @@ int ml2_sample_top_p(ml2_ctx* ctx, const void* values, const int* indices, int s
  * writes tokens[next_pos] and consumes the logits. `coin` is the host's uniform draw in [0,1). */
 int ml2_model_sample(ml2_model* model, int next_pos, float temperature, float top_p, float coin);
 
+/* ---- AWQ checkpoint tensors -> QWeight layout (ModelConverter, src/ModelConverter.cs:196-332) ----------
+ * Device buffers in, device buffers out. Format v0: `in` is an AutoAWQ tensor, int32 [height][width / 8] with the
+ * nibble order map {0,2,4,6,1,3,5,7} (:19); `out` is u32 [width][ceil(height / 8)], 8 consecutive inputs per word
+ * (RepackQData, :286-321; height = d_in for weights, the number of groups for zero points). */
+int ml2_awq_repack_qdata(ml2_ctx* ctx, const uint32_t* in, int height, int width, uint32_t* out);
+/* RepackScales (:323-332): fp16 [meta_height][width] -> [width][meta_height]. */
+int ml2_awq_repack_scales(ml2_ctx* ctx, const void* in, int meta_height, int width, void* out);
+/* Format v1 (:262-275): scales fp16 [width][padded_height] -> [width][scales_size]. */
+int ml2_awq_compact_scales_v1(ml2_ctx* ctx, const void* in, int scales_size, int padded_height, int width, void* out);
+
 /* ---- model.bin reader -------------------------------------------------------------------------
  * Stands for Config.LoadConfig (src/Config.cs:21-31) and the TransformerWeights constructor
  * (src/TransformerWeights.cs:20-41, 54-103): the file written by src/ModelConverter.cs:130-177 is mapped

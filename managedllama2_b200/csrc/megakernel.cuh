@@ -750,9 +750,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                         a = fma_f16_f32(hi16(kv[u].y), hi16(qv.y), a);
                         sc[u] = a;
                     }
-                    transpose_reduce<kAttUnroll>(sc, lane);   // lane 4 * u holds row u
-                    const int u = lane >> 2;
-                    if ((lane & 3) == 0 && b + u < t1) {
+                    transpose_reduce<kAttUnroll>(sc, lane);   // lane (32 / kAttUnroll) * u holds row u
+                    constexpr int kPer = 32 / kAttUnroll;
+                    const int u = lane / kPer;
+                    if ((lane % kPer) == 0 && b + u < t1) {
                         const float sr = __half2float(__float2half_rn(sc[0] * p.scale));
                         s_sc[b + u - t0] = sr;
                         mx = fmaxf(mx, sr);

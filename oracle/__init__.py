@@ -305,3 +305,66 @@ def sample(logits, temperature, top_p, coin):
         probs, idx = sort_desc(probs, idx)
         threshold = np.float32(coin) * np.float32(top_p)
     return sample_top_p(cumulative_sum(probs), idx, threshold)
+
+
+# ---- AWQ -> QWeight repacking (restatement of src/ModelConverter.cs:19, 286-332) ------------------------------
+
+AWQ_ORDER_MAP = (0, 2, 4, 6, 1, 3, 5, 7)   # src/ModelConverter.cs:19
+
+
+def awq_repack_qdata_loops(q_in, height, width):
+    """RepackQData (src/ModelConverter.cs:286-321) as the plain loops it is written in, spare elements of the scratch
+    array included. The reference keeps four (:288), enough for the group counts of Llama-2 (32, 40, 86, 108); a
+    column count whose remainder modulo 8 is 1, 2 or 3 would run past them there. Seven are kept here so that such
+    shapes read zeros instead. ``q_in``: uint32 [height][width / 8]. For small cases."""
+    q_in = np.ascontiguousarray(q_in, np.uint32).reshape(-1)
+    packed = [0] * (width * height + 7)
+    for y in range(height):
+        for x in range(0, width, 8):
+            offset = height * x + y
+            word = int(q_in[(y * width + x) // 8])
+            q = [0] * 8
+            for i in range(8):
+                q[AWQ_ORDER_MAP[i]] = word & 0xF
+                word >>= 4
+            for i in range(8):
+                packed[offset + height * i] = q[i]
+    h8 = (height + 7) // 8
+    out = np.zeros(width * h8, np.uint32)
+    for x in range(width):
+        for y in range(0, height, 8):
+            offset = height * x + y
+            val = 0
+            for i in range(8):
+                val |= packed[offset + i] << (4 * i)
+            out[x * h8 + y // 8] = val
+    return out
+
+
+def awq_repack_qdata(q_in, height, width):
+    """The same, vectorised."""
+    q_in = np.ascontiguousarray(q_in, np.uint32).reshape(height, width // 8)
+    nib = np.zeros((height, width // 8, 8), np.uint32)
+    for j in range(8):
+        nib[:, :, AWQ_ORDER_MAP[j]] = (q_in >> np.uint32(4 * j)) & np.uint32(0xF)
+    vals = nib.reshape(height, width).T.reshape(-1)          # column-major scratch: index = height * x + y
+    h8 = (height + 7) // 8
+    flat = np.concatenate([vals, np.zeros(8, np.uint32)])
+    idx = (np.arange(width)[:, None, None] * height + np.arange(h8)[None, :, None] * 8 + np.arange(8)[None, None, :])
+    idx = np.minimum(idx, vals.size + 7)                      # beyond the last output: the spare zeros
+    g = flat[idx]
+    return (g << (np.arange(8, dtype=np.uint32) * np.uint32(4))[None, None, :]).sum(axis=2, dtype=np.uint64).astype(np.uint32).reshape(-1)
+
+
+def awq_repack_scales(s_in, meta_height, width):
+    """RepackScales (src/ModelConverter.cs:323-332): [meta_height][width] -> [width][meta_height]."""
+    return np.ascontiguousarray(_f16(s_in).reshape(meta_height, width).T).reshape(-1)
+
+
+def awq_pack_v0(values, height, width):
+    """Inverse of the first step: 4-bit ``values`` [height][width] -> AutoAWQ words [height][width / 8] (test helper)."""
+    v = np.asarray(values, np.uint32).reshape(height, width // 8, 8)
+    out = np.zeros((height, width // 8), np.uint32)
+    for j in range(8):
+        out |= (v[:, :, AWQ_ORDER_MAP[j]] & np.uint32(0xF)) << np.uint32(4 * j)
+    return out.reshape(-1)

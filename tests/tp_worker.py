@@ -6,6 +6,8 @@ import sys
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# unit-scale embeddings and norm weights: attention scores of order one, so a wrong score or cache row shows in the logits
+SIGMA = 1.0
 sys.path.insert(0, ROOT)
 
 
@@ -31,11 +33,11 @@ def main():
         sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
         from helpers import write_model_bin
         if rank == 0:
-            write_model_bin(model_bin, cfg, ml2.synthetic_weights_host(cfg, seed=21))
+            write_model_bin(model_bin, cfg, ml2.synthetic_weights_host(cfg, seed=21, sigma=SIGMA))
         dist.barrier()
         tr = ml2.Transformer.FromFile(model_bin, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
     else:
-        w = ml2.synthetic_weights(ctx, cfg, seed=21, tp_size=world, tp_rank=rank)
+        w = ml2.synthetic_weights(ctx, cfg, seed=21, tp_size=world, tp_rank=rank, sigma=SIGMA)
         tr = ml2.Transformer(cfg, w, ctx, tp_size=world, tp_rank=rank, nccl_id=idt.cpu().numpy().tobytes())
     if os.environ.get("ML2_TP_FUSED", "1") == "1":
         tr.attach_peers_with(dist)   # one persistent kernel per token, all-reduce over peer memory
@@ -43,7 +45,7 @@ def main():
     tr.set_tokens(np.array(toks, dtype=np.int32))
     cpu = None
     if rank == 0:
-        hw = ml2.synthetic_weights_host(cfg, seed=21)
+        hw = ml2.synthetic_weights_host(cfg, seed=21, sigma=SIGMA)
         cpu = oracle.CpuModel(dict(dim=cfg.dim, hidden_dim=cfg.hiddenDim, n_layers=cfg.numLayers, n_heads=cfg.numHeads,
                                    n_kv_heads=cfg.numKVHeads, vocab_size=cfg.vocabSize, seq_len=cfg.seqLength,
                                    rope_theta=cfg.ropeTheta), hw, mode=1)
@@ -63,7 +65,7 @@ def main():
         if rank == 0:
             want = cpu.forward(toks[pos], pos).astype(np.float32)
             err = float(np.abs(logits.astype(np.float32) - want).max())
-            ok = ok and err <= 1e-2 and err <= 2e-2 * want.std()
+            ok = ok and err <= 2e-2 * want.std()
     ok = ok and ctx.status() == (0, 0)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
