@@ -242,6 +242,17 @@ int ml2_sample_top_p(ml2_ctx* ctx, const void* values, const int* indices, int s
  * writes tokens[next_pos] and consumes the logits. `coin` is the host's uniform draw in [0,1). */
 int ml2_model_sample(ml2_model* model, int next_pos, float temperature, float top_p, float coin);
 
+/* ---- tokenizer (Tokenizer, src/Tokenizer.cs:27-171); host code, no GPU ------------------------------
+ * `tokenizer.bin`: int32 maxTokenLength, then per piece float score, int32 byte length, UTF-8 bytes (:34-48).
+ * Encode (:95-171): optional BOS, the " " dummy prefix for a non-empty prompt, one token per UTF-16 code unit with
+ * the UTF-8 byte fallback (byte + 3), then the best-scoring adjacent pair is merged until none is a piece; optional
+ * EOS. Decode (:57-86) is stateful like the reference's: <0xNN> pieces are collected until they form characters. */
+typedef struct ml2_tokenizer ml2_tokenizer;
+int ml2_tokenizer_open(const char* path, int vocab_size, ml2_tokenizer** out);
+int ml2_tokenizer_close(ml2_tokenizer* tokenizer);
+int ml2_tokenizer_encode(ml2_tokenizer* tokenizer, const char* prompt_utf8, int bos, int eos, int* out_tokens, int capacity, int* n_out);
+int ml2_tokenizer_decode(ml2_tokenizer* tokenizer, int prev, int token, char* out_utf8, int capacity, int* n_out);
+
 /* ---- AWQ checkpoint tensors -> QWeight layout (ModelConverter, src/ModelConverter.cs:196-332) ----------
  * Device buffers in, device buffers out. Format v0: `in` is an AutoAWQ tensor, int32 [height][width / 8] with the
  * nibble order map {0,2,4,6,1,3,5,7} (:19); `out` is u32 [width][ceil(height / 8)], 8 consecutive inputs per word

@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libml2b200.so")
-SOURCES = ["api.cu", "model.cu", "no_alloc.cu", "model_file.cu", "sampler.cu", "awq_repack.cu"]
+SOURCES = ["api.cu", "model.cu", "no_alloc.cu", "model_file.cu", "sampler.cu", "awq_repack.cu", "tokenizer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr",
