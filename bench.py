@@ -277,13 +277,14 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     tok = tr.read_token(pos)
     barrier()
     t0 = time.perf_counter()
+    out_tok = ctypes.c_int(0)
     for _ in range(args.steps):
         pinned[0] = tok
-        # host -> device: this step's input token
-        _lib.check(tr.lib.ml2_model_put_token_async(tr.handle, pos, ctypes.c_void_p(pinned.data_ptr())))
-        tr.Forward(pos, pos + 1, True)
+        # one C-ABI call per token: host -> device copy of this step's input token, the decode step, device -> host read
+        # of the sampled token (blocking 4-byte read, src/Sampler.cs:69)
+        _lib.check(tr.lib.ml2_model_step_host(tr.handle, pos, ctypes.c_void_p(pinned.data_ptr()), ctypes.byref(out_tok)))
         pos += 1
-        tok = tr.read_token(pos)  # device -> host: the sampled token (blocking 4-byte read, src/Sampler.cs:69)
+        tok = out_tok.value
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     if dist is not None:

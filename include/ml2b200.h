@@ -200,6 +200,10 @@ int ml2_model_set_tokens(ml2_model* model, const int* tokens_host, int first, in
 /* Stream-ordered 4-byte host->device copy of one token id; `token_pinned_host` must stay valid until it ran. */
 int ml2_model_put_token_async(ml2_model* model, int pos, const int* token_pinned_host);
 int ml2_model_read_token(ml2_model* model, int pos, int* token_host);
+/* One greedy decode step with HOST buffers, the per-token body of Transformer.Generate (src/Transformer.cs:96-104):
+ * copies the input token id from (pinned) host memory to tokens[pos], runs Forward(pos, pos + 1) with the greedy
+ * sample, copies tokens[pos + 1] back and waits for it. */
+int ml2_model_step_host(ml2_model* model, int pos, const int* token_in_pinned_host, int* token_out_host);
 int ml2_model_read_logits(ml2_model* model, void* logits_host_f16);
 /* Tensor-parallel persistent kernel (one launch per token per GPU, all-reduce fused into the operator hand-off):
  * every rank owns one peer-visible buffer (counters, fp32 receive zones, logits). `ml2_model_comm_handle` writes

@@ -994,6 +994,22 @@ int ml2_model_put_token_async(ml2_model* h, int pos, const int* token_pinned_hos
     return ML2_OK;
 }
 
+int ml2_model_step_host(ml2_model* h, int pos, const int* token_in_pinned_host, int* token_out_host)
+{
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m || !token_in_pinned_host || !token_out_host) return fail(ML2_E_INVALID, "step_host: null argument");
+    if (pos < 0 || pos + 1 > m->cfg.seq_len) return fail(ML2_E_INVALID, "step_host: pos=%d", pos);
+    if (!m->tokens) return fail(ML2_E_STATE, "step_host: run state missing");
+    // host -> device: this step's input token; the step; device -> host: the sampled token (the reference's blocking
+    // 4-byte read, src/Sampler.cs:69)
+    ML2_CUDA(cudaMemcpyAsync(m->tokens + pos, token_in_pinned_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    const int rc = ml2_model_forward(h, pos, pos + 1, 1);
+    if (rc) return rc;
+    ML2_CUDA(cudaMemcpyAsync(token_out_host, m->tokens + pos + 1, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    return ML2_OK;
+}
+
 int ml2_model_read_token(ml2_model* h, int pos, int* token_host)
 {
     Model* m = reinterpret_cast<Model*>(h);

@@ -189,3 +189,30 @@ def test_peaked_attention_matches_oracle(mode):
     assert ctx.status() == (0, 0)
     tr.close()
     ctx.close()
+
+
+def test_step_host_equals_forward_and_read():
+    """ml2_model_step_host (token in from host memory, step, token out) gives the tokens of Forward + read_token."""
+    import ctypes
+    import torch
+    import managedllama2_b200 as ml2
+    from managedllama2_b200 import _lib
+    cfg = small_config(ml2)
+    ctx = ml2.CudaContext(0)
+    w = ml2.synthetic_weights(ctx, cfg, seed=8, sigma=1.0)
+    a, b = ml2.Transformer(cfg, w, ctx), ml2.Transformer(cfg, w, ctx)
+    a.set_tokens(np.array([7], np.int32))
+    pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+    out = ctypes.c_int(0)
+    tok_a, tok_b = 7, 7
+    for pos in range(20):
+        a.set_tokens(np.array([tok_a], np.int32), first=pos)
+        a.Forward(pos, pos + 1, True)
+        tok_a = a.read_token(pos + 1)
+        pinned[0] = tok_b
+        _lib.check(b.lib.ml2_model_step_host(b.handle, pos, ctypes.c_void_p(pinned.data_ptr()), ctypes.byref(out)))
+        tok_b = out.value
+        assert tok_a == tok_b, pos
+    a.close()
+    b.close()
+    ctx.close()
