@@ -215,8 +215,9 @@ int ml2_model_read_logits(ml2_model* model, void* logits_host_f16);
  * ml2_model_forward the same number of times. */
 int ml2_model_comm_handle(ml2_model* model, void* out64);
 int ml2_model_comm_attach(ml2_model* model, const void* handles_rank_order, int n_ranks);
-/* Diagnostics: per-CTA cycle counters of the last persistent-kernel launch (16 values per CTA: total, dependency
- * waits, ring waits, partial-slot waits, attention, prologue); needs ML2_MEGA_PROF=1 in the environment. */
+/* Diagnostics: per-CTA cycle counters of the last persistent-kernel launch, 64 values per CTA ([0..5] total,
+ * dependency waits, ring waits, partial-slot waits, attention, prologue; [8..31] wait / prologue / tile cycles per
+ * operator kind; [32..43] producer and finalizer busy and wait cycles); needs ML2_MEGA_PROF=1 in the environment. */
 int ml2_model_debug_prof(ml2_model* model, long long* out, int n);
 /* The CUDA stream the model launches on (for events or for ordering other work after it). */
 int ml2_model_stream(ml2_model* model, void** cuda_stream);

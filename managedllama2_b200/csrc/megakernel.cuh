@@ -13,17 +13,17 @@
 //   * finalizer warps sum the k-warp partials in a fixed order and run the operator's tail (residual add, RoPE,
 //                     SwiGLU, stores) with the reference's fp16 rounding points; after its last tile of an
 //                     operator a CTA publishes "my share is done" (release) on that operator's counter.
-//   * attention       is an operator without weights: CTA h handles head h with the same three steps and rounding
-//                     points as the reference's scores / softmax / values kernels.
+//   * attention       is an operator without weights, with the three steps and rounding points of the reference's
+//                     scores / softmax / values kernels: one CTA per head for short contexts, several CTAs per head
+//                     (parts of the sequence, maximum / exp-sum exchanged through global memory) for long ones.
+//   * wide rows       (down-projection) are swept several times by a group of fewer warps, the prepared input
+//                     slices parked in shared memory, so that all warps stay busy (mega_multisweep_op).
 //
 // Every wait is bounded; when a limit runs out the CTA records an error word, stops waiting and runs to its end.
 #pragma once
 
 #include "stream_matvec.cuh"
 
-#ifndef ML2_CW
-#define ML2_CW 21
-#endif
 #ifndef ML2_MULTI
 #define ML2_MULTI 1
 #endif
@@ -92,7 +92,7 @@ struct MegaParams {
     long long* prof;           // optional [gridDim.x][64] cycle counters (diagnostics), may be null
 };
 
-constexpr int kMegaConsumerWarps = ML2_CW;
+constexpr int kMegaConsumerWarps = 21;   // 3 groups of 7, 4 of 5, 5 of 4
 constexpr int kMegaFinalWarps = 2;
 constexpr int kMegaWarps = kMegaConsumerWarps + 1 + kMegaFinalWarps;
 constexpr int kMegaThreads = kMegaWarps * 32;

@@ -265,16 +265,13 @@ __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, vo
     }
 }
 
-#ifndef ML2_PARK_NS
-#define ML2_PARK_NS 20000u
-#endif
 // The same for roles off the critical path (producer, finalizers): the hardware parks the thread between polls,
 // so a waiting warp does not take issue slots from the arithmetic warps.
 __device__ __forceinline__ void wait_parked_or_abort(uint64_t* bar, uint32_t parity, volatile unsigned int* abort_flag,
                                                      DeviceStatus* status, unsigned int code, int tile)
 {
     for (uint32_t i = 0; i < (kSpinLimit >> 6); ++i) {
-        if (mbar_try_wait_suspend(bar, parity, ML2_PARK_NS)) return;
+        if (mbar_try_wait_suspend(bar, parity, 20000u)) return;
         if ((i & 15u) == 15u && *abort_flag) return;
     }
     *abort_flag = 1;
