@@ -294,6 +294,12 @@ int ml2_model_file_close(ml2_model_file* file);
 int ml2_model_file_config(const ml2_model_file* file, ml2_config* out);
 /* Pointer into the mapping and byte length of one array of the file. */
 int ml2_model_file_tensor(const ml2_model_file* file, int layer, int tensor, int part, const void** data, uint64_t* bytes);
+/* Host-only: the part of one QWeight (tensor ML2_T_QUERY .. ML2_T_DOWN) that rank `tp_rank` of `tp_size` owns, copied
+ * into caller buffers (any of them may be null to ask for the sizes only). Outputs of query / key / value / up / gate
+ * are cut by range; inputs of output / down as a window of whole groups of 128, zero points re-packed from the
+ * window's first group. */
+int ml2_model_file_shard(const ml2_model_file* file, int layer, int tensor, int tp_size, int tp_rank, void* weight_out, void* zeros_out,
+                         void* scales_out, uint64_t* weight_bytes, uint64_t* zeros_bytes, uint64_t* scales_bytes);
 /* Stands for the host-to-device copies of the Transformer constructor (src/Transformer.cs:58-61 and the
  * CudaDeviceVariable assignments of src/TransformerWeights.cs): copies the shard that rank `tp_rank` of `tp_size`
  * owns into one device allocation (outputs of query / key / value / gate / up and vocabulary rows by range, inputs

@@ -217,11 +217,11 @@ void shard_sizes(const QSpan& q, const Shard& sh, uint64_t* bw, uint64_t* bz, ui
     *rows_local = rows;
 }
 
-// Copies the shard of `q` into the arena. A column range is contiguous in all three arrays; a window of groups is cut
-// out of every column (weights: 16 words per group; scales: one per group; zero points: re-packed so that the
-// window's first group sits in nibble 0 of word 0).
-int upload_qweight(const ml2_model_file* f, const QSpan& q, const Shard& sh, unsigned char* arena, const Placed& at,
-                   std::vector<unsigned char>& tmp)
+// The shard of `q` as three host pointers. A column range is contiguous in all three arrays of the file (the pointers
+// then point into the mapping); a window of groups is cut out of every column into `tmp` (weights: 16 words per group;
+// scales: one per group; zero points: re-packed so that the window's first group sits in nibble 0 of word 0).
+void cut_qweight(const ml2_model_file* f, const QSpan& q, const Shard& sh, std::vector<unsigned char>& tmp, const void** pw, const void** pz,
+                 const void** ps, uint64_t* bw_out, uint64_t* bz_out, uint64_t* bs_out)
 {
     const unsigned char* fw = f->base + q.w.off;
     const unsigned char* fz = f->base + q.z.off;
@@ -230,12 +230,13 @@ int upload_qweight(const ml2_model_file* f, const QSpan& q, const Shard& sh, uns
     uint64_t bw, bz, bs;
     int rows_local;
     shard_sizes(q, sh, &bw, &bz, &bs, &rows_local);
+    *bw_out = bw; *bz_out = bz; *bs_out = bs;
     const bool window = sh.ngroups >= 0 && !(sh.g0 == 0 && rows_local == q.rows);
     if (!window) {
-        ML2_CUDA(cudaMemcpy(arena + at.w, fw + (uint64_t)sh.col0 * wsize_f * 4, bw, cudaMemcpyHostToDevice));
-        ML2_CUDA(cudaMemcpy(arena + at.z, fz + (uint64_t)sh.col0 * zsize_f * 4, bz, cudaMemcpyHostToDevice));
-        ML2_CUDA(cudaMemcpy(arena + at.s, fs + (uint64_t)sh.col0 * ssize_f * 2, bs, cudaMemcpyHostToDevice));
-        return ML2_OK;
+        *pw = fw + (uint64_t)sh.col0 * wsize_f * 4;
+        *pz = fz + (uint64_t)sh.col0 * zsize_f * 4;
+        *ps = fs + (uint64_t)sh.col0 * ssize_f * 2;
+        return;
     }
     const uint64_t ng = (uint64_t)cdiv(rows_local, kGroupRows);
     const uint64_t wsize_l = (uint64_t)cdiv(rows_local, 32) * 4, zsize_l = (ng + 7) / 8;
@@ -257,10 +258,40 @@ int upload_qweight(const ml2_model_file* f, const QSpan& q, const Shard& sh, uns
             dz[j >> 3] |= nib << (4 * (j & 7));
         }
     }
-    ML2_CUDA(cudaMemcpy(arena + at.w, tw, bw, cudaMemcpyHostToDevice));
-    ML2_CUDA(cudaMemcpy(arena + at.z, tz, bz, cudaMemcpyHostToDevice));
-    ML2_CUDA(cudaMemcpy(arena + at.s, ts, bs, cudaMemcpyHostToDevice));
+    *pw = tw;
+    *pz = tz;
+    *ps = ts;
+}
+
+int upload_qweight(const ml2_model_file* f, const QSpan& q, const Shard& sh, unsigned char* arena, const Placed& at,
+                   std::vector<unsigned char>& tmp)
+{
+    const void *pw, *pz, *ps;
+    uint64_t bw, bz, bs;
+    cut_qweight(f, q, sh, tmp, &pw, &pz, &ps, &bw, &bz, &bs);
+    ML2_CUDA(cudaMemcpy(arena + at.w, pw, bw, cudaMemcpyHostToDevice));
+    ML2_CUDA(cudaMemcpy(arena + at.z, pz, bz, cudaMemcpyHostToDevice));
+    ML2_CUDA(cudaMemcpy(arena + at.s, ps, bs, cudaMemcpyHostToDevice));
     return ML2_OK;
+}
+
+// shard geometry of the seven QWeights of a layer (file order) for one rank; false when the shapes do not split
+bool layer_shards(const ml2_config& c, int tp_size, int tp_rank, Shard (&shards)[7], int* hidden_local_out)
+{
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return false;
+    if (c.n_heads % tp_size || c.vocab_size % tp_size || (c.dim / tp_size) % kGroupRows || (tp_size > 1 && c.hidden_dim % kGroupRows)) return false;
+    const int dim_local = c.dim / tp_size;
+    int hg0 = 0, hng = 0;
+    ml2_tp_hidden_groups(c.hidden_dim, tp_size, tp_rank, &hg0, &hng);
+    const int hidden_local = tp_size == 1 ? c.hidden_dim : hng * kGroupRows;
+    const Shard sq{tp_rank * dim_local, dim_local, 0, -1};
+    const Shard so{0, c.dim, tp_rank * (dim_local / kGroupRows), tp_size == 1 ? -1 : dim_local / kGroupRows};
+    const Shard sf{tp_size == 1 ? 0 : hg0 * kGroupRows, hidden_local, 0, -1};
+    const Shard sd{0, c.dim, hg0, tp_size == 1 ? -1 : hng};
+    const Shard all[7] = {sq, sq, sq, so, sf, sf, sd};
+    for (int i = 0; i < 7; ++i) shards[i] = all[i];
+    if (hidden_local_out) *hidden_local_out = hidden_local;
+    return true;
 }
 
 }  // namespace
@@ -277,17 +308,9 @@ int ml2_weights_upload(ml2_ctx* h, const ml2_model_file* f, int tp_size, int tp_
     if (c.n_heads % tp_size || c.vocab_size % tp_size || (c.dim / tp_size) % kGroupRows || (tp_size > 1 && c.hidden_dim % kGroupRows))
         return fail(ML2_E_INVALID, "weights_upload: heads=%d vocab=%d dim=%d hidden=%d do not split over %d ranks", c.n_heads, c.vocab_size,
                     c.dim, c.hidden_dim, tp_size);
-    const int dim_local = c.dim / tp_size, vocab_local = c.vocab_size / tp_size;
-    int hg0 = 0, hng = 0;
-    ml2_tp_hidden_groups(c.hidden_dim, tp_size, tp_rank, &hg0, &hng);
-    const int hidden_local = tp_size == 1 ? c.hidden_dim : hng * kGroupRows;
-
-    // shard of each of the seven QWeights, in file order
-    const Shard sq{tp_rank * dim_local, dim_local, 0, -1};
-    const Shard so{0, c.dim, tp_rank * (dim_local / kGroupRows), tp_size == 1 ? -1 : dim_local / kGroupRows};
-    const Shard sf{tp_size == 1 ? 0 : hg0 * kGroupRows, hidden_local, 0, -1};
-    const Shard sd{0, c.dim, hg0, tp_size == 1 ? -1 : hng};
-    const Shard shards[7] = {sq, sq, sq, so, sf, sf, sd};
+    const int vocab_local = c.vocab_size / tp_size;
+    Shard shards[7];
+    layer_shards(c, tp_size, tp_rank, shards, nullptr);
 
     // arena layout
     uint64_t total = 0;
@@ -408,5 +431,27 @@ int ml2_weights_free(ml2_weights* w)
         cudaFree(w->arena);
     }
     delete w;
+    return ML2_OK;
+}
+
+int ml2_model_file_shard(const ml2_model_file* f, int layer, int tensor, int tp_size, int tp_rank, void* weight_out, void* zeros_out,
+                         void* scales_out, uint64_t* weight_bytes, uint64_t* zeros_bytes, uint64_t* scales_bytes)
+{
+    if (!f) return fail(ML2_E_INVALID, "model_file_shard: null file");
+    if (layer < 0 || layer >= (int)f->layers.size() || tensor < ML2_T_QUERY || tensor > ML2_T_DOWN)
+        return fail(ML2_E_INVALID, "model_file_shard: layer %d tensor %d", layer, tensor);
+    Shard shards[7];
+    if (!layer_shards(f->cfg, tp_size, tp_rank, shards, nullptr))
+        return fail(ML2_E_INVALID, "model_file_shard: the model does not split over %d ranks (rank %d)", tp_size, tp_rank);
+    std::vector<unsigned char> tmp;
+    const void *pw, *pz, *ps;
+    uint64_t bw, bz, bs;
+    cut_qweight(f, f->layers[(size_t)layer].q[tensor - ML2_T_QUERY], shards[tensor - ML2_T_QUERY], tmp, &pw, &pz, &ps, &bw, &bz, &bs);
+    if (weight_bytes) *weight_bytes = bw;
+    if (zeros_bytes) *zeros_bytes = bz;
+    if (scales_bytes) *scales_bytes = bs;
+    if (weight_out) memcpy(weight_out, pw, (size_t)bw);
+    if (zeros_out) memcpy(zeros_out, pz, (size_t)bz);
+    if (scales_out) memcpy(scales_out, ps, (size_t)bs);
     return ML2_OK;
 }

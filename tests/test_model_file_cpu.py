@@ -83,3 +83,52 @@ def test_bad_tensor_requests(model):
         for args in ((-1, 3, 0), (0, 9, 0), (2, 0, 0), (0, T.T_QUERY, 3), (0, T.T_RMS_ATT, 1)):
             with pytest.raises(ml2.Ml2Error):
                 mf.tensor(*args)
+
+
+@pytest.mark.parametrize("tp", [1, 2])
+def test_shards_cut_on_the_host_equal_generated_shards(model, tp):
+    """ml2_model_file_shard (no GPU): every rank's part of every QWeight equals the shard the synthetic generator makes
+    in place for the same rank - column ranges for query / key / value / up / gate, windows of groups with re-packed
+    zero points for output / down (5 hidden groups over 2 ranks: 3 + 2, an uneven split)."""
+    import ctypes
+    from managedllama2_b200 import _lib
+    from managedllama2_b200.transformer import GROUP, layer_tid, tp_shapes, _qw_window
+    path, _ = model
+    lib = _lib.load()
+    dim, hid = CFG.dim, CFG.hiddenDim
+    with ml2.ModelFile(path) as mf:
+        for rank in range(tp):
+            dim_local, hg0, hng, _, _ = tp_shapes(CFG, tp, rank)
+            hidden_local = hng * GROUP
+            gd = dim // GROUP
+            # (tensor id in the file, generator name, rows_full, col0, ncols, g0, ngroups)
+            plan = [(T.T_QUERY, "query", dim, rank * dim_local, dim_local, 0, gd), (T.T_KEY, "key", dim, rank * dim_local, dim_local, 0, gd),
+                    (T.T_VALUE, "value", dim, rank * dim_local, dim_local, 0, gd),
+                    (T.T_OUTPUT, "output", dim, 0, dim, rank * (dim_local // GROUP), dim_local // GROUP),
+                    (T.T_UP, "up", dim, hg0 * GROUP, hidden_local, 0, gd), (T.T_GATE, "gate", dim, hg0 * GROUP, hidden_local, 0, gd),
+                    (T.T_DOWN, "down", hid, 0, dim, hg0, hng)]
+            for l in range(CFG.numLayers):
+                for tid, name, rows_full, col0, ncols, g0, ng in plan:
+                    _, nw, nz, ns = _qw_window(rows_full, ncols, g0, ng)
+                    w, z, s = np.empty(nw, np.uint32), np.empty(nz, np.uint32), np.empty(ns, np.float16)
+                    _lib.check(lib.ml2_synth_qweight_host(w.ctypes.data_as(ctypes.c_void_p), z.ctypes.data_as(ctypes.c_void_p),
+                                                          s.ctypes.data_as(ctypes.c_void_p), rows_full, col0, ncols, g0, ng,
+                                                          ctypes.c_uint64(5), ctypes.c_uint32(layer_tid(l, name))))
+                    bw, bz, bs = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+                    _lib.check(lib.ml2_model_file_shard(mf.handle, l, tid, tp, rank, None, None, None, ctypes.byref(bw), ctypes.byref(bz),
+                                                        ctypes.byref(bs)))
+                    assert (bw.value, bz.value, bs.value) == (nw * 4, nz * 4, ns * 2), (rank, l, name)
+                    gw, gz, gs = np.empty(nw, np.uint32), np.empty(nz, np.uint32), np.empty(ns, np.float16)
+                    _lib.check(lib.ml2_model_file_shard(mf.handle, l, tid, tp, rank, gw.ctypes.data_as(ctypes.c_void_p),
+                                                        gz.ctypes.data_as(ctypes.c_void_p), gs.ctypes.data_as(ctypes.c_void_p), None, None, None))
+                    assert np.array_equal(gw, w), (rank, l, name)
+                    assert np.array_equal(gs.view(np.uint16), s.view(np.uint16)), (rank, l, name)
+                    zs = (ng + 7) // 8
+                    mask = np.zeros(zs, np.uint32)
+                    for g in range(ng):
+                        mask[g // 8] |= np.uint32(0xF << (4 * (g % 8)))
+                    m = np.tile(mask, nz // zs)
+                    assert np.array_equal(gz & m, z & m), (rank, l, name)
+        with pytest.raises(ml2.Ml2Error):
+            lib_rc = lib.ml2_model_file_shard(mf.handle, 0, T.T_QUERY, 3, 0, None, None, None, None, None, None)
+            _lib.check(lib_rc)
