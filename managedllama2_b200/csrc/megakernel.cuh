@@ -24,17 +24,6 @@
 
 #include "stream_matvec.cuh"
 
-#ifndef ML2_TILE_CALL
-#define ML2_TILE_CALL 0
-#endif
-#ifndef ML2_MULTI_CALL
-#define ML2_MULTI_CALL 0
-#endif
-#if ML2_MULTI_CALL
-#define ML2_MULTI_ATTR __noinline__
-#else
-#define ML2_MULTI_ATTR __forceinline__
-#endif
 #ifndef ML2_MULTI
 #define ML2_MULTI 1
 #endif
@@ -325,7 +314,7 @@ struct MegaShared {
 // Every lane slot's prepared slice is built once per operator and parked in shared memory; a group of kw warps sweeps
 // a tile `passes` times, reloading the lane's slice per sweep, so that groups * kw warps stay busy where a single
 // sweep would tie most of the warps to one row. A loop of its own, apart from the single-sweep loop of the kernel.
-__device__ ML2_MULTI_ATTR void mega_multisweep_op(const MegaOp& op, int k, const MegaShared& sh, int first, int cnt, uint32_t n_base,
+__device__ __forceinline__ void mega_multisweep_op(const MegaOp& op, int k, const MegaShared& sh, int first, int cnt, uint32_t n_base,
                                                    int st_base, uint32_t ph_base)
 {
     constexpr int kConsThreads = kMegaConsumerWarps * 32;
@@ -416,119 +405,6 @@ __device__ ML2_MULTI_ATTR void mega_multisweep_op(const MegaOp& op, int k, const
         if (lane == 0) mbar_arrive_n(&sh.done_bar[slot], my_arrive);
         st += op.groups;
         while (st >= sh.nstage) { st -= sh.nstage; ph ^= 1u; }
-    }
-}
-
-// Arguments of the single-sweep tile loop when it runs as a function of its own (see mega_singlesweep_tiles).
-struct MegaTileArgs {
-    int kind, nch, rwc, run_rows, cols, kw, groups;
-    uint32_t chunk_bytes;
-    __half* out0;
-    int first, cnt, ncta, group, kw_id, k;
-    bool in_group, active, is_int4;
-    uint32_t w_off, z_off, s_off, w_row, z_row, s_row, ring, my_arrive;
-    int zshift;
-    int st_base;
-    uint32_t ph_base, n_base;
-    int nstage, slot_bytes, debug;
-    DeviceStatus* status;
-    uint64_t* full_bar;
-    uint64_t* empty_bar;
-    uint64_t* done_bar;
-    uint64_t* free_bar;
-    float* red;
-    unsigned int* abort_flag;
-};
-
-// The tile loop of a single-sweep operator (input slice stationary in registers). Out of line on purpose: the loop
-// sits at the register limit, and compiled inside the kernel its allocation shifts with every other code path of the
-// kernel (measured: 2-25 % of the token rate); as a function it is allocated on its own.
-__device__ __noinline__ void mega_singlesweep_tiles(const MegaTileArgs a, const XSlice xs)
-{
-    const int lane = threadIdx.x & 31;
-    // tiles i = group, group + groups, ... belong to this group (idle warps take none)
-    int st = a.st_base + a.group;
-    uint32_t ph = a.ph_base;
-    while (st >= a.nstage) { st -= a.nstage; ph ^= 1u; }
-    for (int i = a.group; a.in_group && i < a.cnt; i += a.groups) {
-        const uint32_t n = a.n_base + (uint32_t)i;
-        wait_or_abort(&a.full_bar[st], ph, a.abort_flag, a.status, 2u, a.k);
-        const int slot = (int)(n % kMegaRedSlots);
-        float* red = a.red + (size_t)slot * (kMaxKW * kMegaMaxRows);
-        bool slot_ready = n < (uint32_t)kMegaRedSlots;
-        float resid[2] = {0.f, 0.f};
-        if (a.kind == MOP_RESID && a.kw_id == 0 && (lane & 7) == 0 && (lane >> 3) < a.rwc) {
-            const int tile = a.first + i * a.ncta;
-            for (int c = 0; c < a.nch; ++c) {
-                const int row = (tile * a.nch + c) * a.rwc + (lane >> 3);
-                if (row < a.cols) resid[c] = __half2float(a.out0[row]);
-            }
-        }
-        for (int c = 0; c < a.nch; ++c) {
-            // chunk c = rows [c*rwc, c*rwc + rwc) of the tile; they sit in run (c*rwc / run_rows) at row rin0 of that run
-            const int trow = c * a.rwc;
-            const int run = (a.run_rows == 8) ? (trow >> 3) : (a.run_rows == 4 ? (trow >> 2) : (trow >> 1));
-            const int rin0 = trow - run * a.run_rows;
-            const uint32_t cbase = a.ring + (uint32_t)st * a.slot_bytes + (uint32_t)run * a.chunk_bytes;
-            const uint32_t cb = cbase;   // weights of the run start here
-            const uint32_t cw = cbase + (uint32_t)rin0 * a.w_row;
-            const uint32_t cz = cbase + (uint32_t)rin0 * a.z_row;
-            const uint32_t cs = cbase + (uint32_t)rin0 * a.s_row;
-            (void)cb;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (a.debug & 1) {
-            } else if (a.is_int4) {
-                mega_int4_rows(xs, cw + a.w_off, cz + a.z_off, cs + a.s_off, a.w_row, a.z_row, a.s_row, a.zshift, a.active, v);
-            } else {
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    if (r < a.rwc) {
-                        uint4 wv, wu;
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
-                                     : "r"(cw + a.w_off + r * a.w_row));
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(wu.x), "=r"(wu.y), "=r"(wu.z), "=r"(wu.w)
-                                     : "r"(cw + a.w_off + r * a.w_row + 16u));
-                        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-                        a0 = fma_f16_f32(lo16(wv.x), lo16(xs.xp[0]), a0);
-                        a1 = fma_f16_f32(hi16(wv.x), hi16(xs.xp[0]), a1);
-                        a2 = fma_f16_f32(lo16(wv.y), lo16(xs.xp[1]), a2);
-                        a3 = fma_f16_f32(hi16(wv.y), hi16(xs.xp[1]), a3);
-                        a0 = fma_f16_f32(lo16(wv.z), lo16(xs.xp[2]), a0);
-                        a1 = fma_f16_f32(hi16(wv.z), hi16(xs.xp[2]), a1);
-                        a2 = fma_f16_f32(lo16(wv.w), lo16(xs.xp[3]), a2);
-                        a3 = fma_f16_f32(hi16(wv.w), hi16(xs.xp[3]), a3);
-                        a0 = fma_f16_f32(lo16(wu.x), lo16(xs.xp[4]), a0);
-                        a1 = fma_f16_f32(hi16(wu.x), hi16(xs.xp[4]), a1);
-                        a2 = fma_f16_f32(lo16(wu.y), lo16(xs.xp[5]), a2);
-                        a3 = fma_f16_f32(hi16(wu.y), hi16(xs.xp[5]), a3);
-                        a0 = fma_f16_f32(lo16(wu.z), lo16(xs.xp[6]), a0);
-                        a1 = fma_f16_f32(hi16(wu.z), hi16(xs.xp[6]), a1);
-                        a2 = fma_f16_f32(lo16(wu.w), lo16(xs.xp[7]), a2);
-                        a3 = fma_f16_f32(hi16(wu.w), hi16(xs.xp[7]), a3);
-                        v[r] = a.active ? ((a0 + a1) + (a2 + a3)) : 0.f;
-                    }
-                }
-            }
-            if (c == a.nch - 1) {
-                // last read of the stage by this warp: hand it back to the producer
-                __syncwarp();
-                if (lane == 0) mbar_arrive_n(&a.empty_bar[st], a.my_arrive);
-            }
-            if (!(a.debug & 2)) transpose_reduce<4>(v, lane);
-            if (!slot_ready) {
-                wait_or_abort(&a.free_bar[slot], ((n / kMegaRedSlots) - 1u) & 1u, a.abort_flag, a.status, 4u, a.k);
-                slot_ready = true;
-            }
-            if ((lane & 7) == 0 && (lane >> 3) < a.rwc) red[a.kw_id * kMegaMaxRows + c * a.rwc + (lane >> 3)] = v[0];
-            if (a.kind == MOP_RESID && a.kw_id == 0 && (lane & 7) == 0 && (lane >> 3) < a.rwc)
-                red[a.kw * kMegaMaxRows + c * a.rwc + (lane >> 3)] = resid[c];
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive_n(&a.done_bar[slot], a.my_arrive);
-        st += a.groups;
-        while (st >= a.nstage) { st -= a.nstage; ph ^= 1u; }
     }
 }
 
@@ -1151,19 +1027,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         // arrival weights: the fixed barrier count is met by (kw - 1) single arrivals + one weighted arrival per tile
         const uint32_t my_arrive = (kw_id == 0) ? (kBarCount - (uint32_t)op.kw + 1u) : 1u;
 
-        if (!kProf && ML2_TILE_CALL) {
-            MegaTileArgs ta;
-            ta.kind = op.kind; ta.nch = op.nch; ta.rwc = op.rwc; ta.run_rows = op.run_rows; ta.cols = op.cols; ta.kw = op.kw; ta.groups = op.groups;
-            ta.chunk_bytes = (uint32_t)op.chunk_bytes; ta.out0 = op.out[0];
-            ta.first = first; ta.cnt = cnt; ta.ncta = ncta; ta.group = group; ta.kw_id = kw_id; ta.k = k;
-            ta.in_group = in_group; ta.active = active; ta.is_int4 = is_int4;
-            ta.w_off = w_off; ta.z_off = z_off; ta.s_off = s_off; ta.w_row = w_row; ta.z_row = z_row; ta.s_row = s_row; ta.ring = ring;
-            ta.my_arrive = my_arrive; ta.zshift = zshift; ta.st_base = st_base; ta.ph_base = ph_base; ta.n_base = n_base;
-            ta.nstage = p.nstage; ta.slot_bytes = p.slot_bytes; ta.debug = p.debug; ta.status = p.status;
-            ta.full_bar = full_bar; ta.empty_bar = empty_bar; ta.done_bar = done_bar; ta.free_bar = free_bar;
-            ta.red = &s_red[0][0][0]; ta.abort_flag = &s_abort;
-            mega_singlesweep_tiles(ta, xs);
-        } else {
         // tiles i = group, group + groups, ... belong to this group (idle warps take none)
         int st = st_base + group;
         uint32_t ph = ph_base;
@@ -1250,7 +1113,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             if (lane == 0) mbar_arrive_n(&done_bar[slot], my_arrive);
             st += op.groups;
             while (st >= p.nstage) { st -= p.nstage; ph ^= 1u; }
-        }
         }
         tk_run[kk] += now() - trun0;
         n_base += (uint32_t)cnt;
