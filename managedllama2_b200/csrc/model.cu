@@ -186,7 +186,7 @@ struct Model {
     float* att_part = nullptr;
     unsigned int* att_cnt = nullptr;
     int att_split = 1;                      // CTAs per head when the split path is taken (1: never)
-    int att_min_seq = 384;                  // shortest sequence that takes it
+    int att_min_seq = 704;                  // shortest sequence that takes it
     unsigned int att_seq = 0;
     // tensor parallel persistent kernel: one peer-visible buffer per rank (counters, receive zones, logits)
     void* comm_local = nullptr;

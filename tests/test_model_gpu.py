@@ -114,7 +114,7 @@ def test_generate_host_api_and_determinism():
 
 
 def test_long_sequence_cluster_path():
-    """Sequence longer than the single-CTA limit: the cluster path (DSMEM exchange) against the oracle."""
+    """A sequence of 400 positions (one CTA per head in the persistent kernel) against the oracle."""
     import managedllama2_b200 as ml2
     cfg = ml2.Config(dim=256, hiddenDim=384, numLayers=1, numHeads=2, numKVHeads=2, vocabSize=256, seqLength=400)
     ctx = ml2.CudaContext(0)
