@@ -739,7 +739,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     uint2 kv[kAttUnroll];
 #pragma unroll
                     for (int u = 0; u < kAttUnroll; ++u)
-                        kv[u] = (b + u < t1) ? *reinterpret_cast<const uint2*>(kh + (size_t)(b + u) * stride) : make_uint2(0u, 0u);
+                        kv[u] = *reinterpret_cast<const uint2*>(kh + (size_t)min(b + u, t1 - 1) * stride);   // unconditional: all loads in flight together
                     float sc[kAttUnroll];
 #pragma unroll
                     for (int u = 0; u < kAttUnroll; ++u) {
@@ -805,7 +805,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     uint2 vv[kAttUnroll];
 #pragma unroll
                     for (int u = 0; u < kAttUnroll; ++u)
-                        vv[u] = (b + u < t1) ? *reinterpret_cast<const uint2*>(vh + (size_t)(b + u) * stride) : make_uint2(0u, 0u);
+                        vv[u] = *reinterpret_cast<const uint2*>(vh + (size_t)min(b + u, t1 - 1) * stride);
 #pragma unroll
                     for (int u = 0; u < kAttUnroll; ++u) {
                         if (b + u < t1) {
