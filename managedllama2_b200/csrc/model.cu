@@ -178,6 +178,7 @@ struct Model {
     int mega_nops = 0, mega_nstage = 0, mega_slot = 0, mega_att_bytes = 0, mega_smem = 0, mega_grid = 0;
     unsigned int mega_seq = 0;
     long long* mega_prof = nullptr;
+    bool want_prof = false;                 // cycle counters of the diagnostic instantiation (ML2_MEGA_PROF=1 at model creation)
     unsigned int* mega_done_ptr = nullptr;
     __half* logits_view = nullptr;          // where the full logits of the persistent kernel land
     int* sample_indices = nullptr;          // token ids carried through the sampler's sort (RunState.indices)
@@ -405,61 +406,75 @@ static double qweight_bytes(int rows, int cols)
 }
 
 // ---- persistent per-token kernel: operator list and launch ------------------------------------------------------
-static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, bool paired, bool plain_input = false)
+// Plans one weight operator for a ring slot of `slot_bytes`: lane mapping (warps per group, groups, weight vectors per
+// lane), the alignment granule of its rows and the rows of a full tile.
+static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, int nmat, bool paired, int slot_bytes)
 {
     op.fmt = fmt;
     op.rows = rows;
     op.cols = cols;
+    op.nmat = nmat;
+    op.paired = paired ? 1 : 0;
     op.tp = 1;
+    op.has_tiles = 1;
     if (fmt == 0) {
-        op.ssize = ceil_div(rows, kGroup);
-        op.wsize = ceil_div(rows, 32) * 4;
-        op.zsize = ceil_div(op.ssize, 8);
         if (rows % 32) return false;
-        op.rwc = 4;
-        // a 4-row run of scales is 8*ssize bytes: with an odd group count only 8-row runs keep every bulk copy
-        // 16-byte aligned (paired tiles cannot use them: their two runs belong to different matrices / row blocks)
-        const bool odd = (op.ssize & 1) != 0;
-        if (odd && paired) return false;
-        op.run_rows = odd ? 8 : 4;
-        op.nruns = paired ? 2 : 1;
-        op.nch = paired ? 2 : op.run_rows / 4;
+        const int ssize = ceil_div(rows, kGroup), wsize = ceil_div(rows, 32) * 4, zsize = ceil_div(ssize, 8);
+        op.wrow = wsize * 4;
+        op.zrow = zsize * 4;
+        op.srow = ssize * 2;
+        op.units = wsize / 4;
     } else {
-        if (rows % 16) return false;   // a lane owns two 16-byte vectors of every fp16 row
-        op.wsize = rows / 2;
-        op.zsize = op.ssize = 0;
-        op.rwc = (rows * 2 * 4 <= 24 * 1024) ? 4 : 2;
-        op.run_rows = op.rwc;
-        op.nruns = 1;
-        op.nch = 1;
+        if (rows % 8) return false;
+        op.wrow = rows * 2;
+        op.zrow = op.srow = 0;
+        op.units = rows / 8;
     }
-    if (cols % op.run_rows) return false;
-    op.units = fmt == 0 ? op.wsize / 4 : op.wsize / 8;   // lane slots per row
-    // Warps per group and sweeps per row: a group of kw warps covers a row in `passes` sweeps of kw * 32 lane slots
-    // and `groups` groups work side by side, so the rate is proportional to groups / passes. One sweep keeps the
-    // input slice in registers; more sweeps reload prepared slices from shared memory (int4 operators whose input
-    // needs no normalisation only), which keeps all warps busy when a row is wider than a third of the lanes.
+    // every bulk copy of a tile (rows x bytes per row, in each of the three arrays) must be a multiple of 16 bytes
+    auto rows_for_16 = [](int row_bytes) {
+        int n = 1;
+        while ((n * row_bytes) % 16) n *= 2;
+        return n;
+    };
+    op.gran = std::max(rows_for_16(op.wrow), std::max(op.zrow ? rows_for_16(op.zrow) : 1, op.srow ? rows_for_16(op.srow) : 1));
+    if (cols % op.gran) return false;
+    // Lane mapping: a group of kw warps spans a row with np weight vectors per lane; G groups share every tile. The
+    // best mapping keeps the most lanes busy: (row coverage) x (warps in a group).
     op.kw = 0;
-    op.passes = 1;
-    op.groups = 0;
-    const bool multi = fmt == 0 && plain_input && !getenv("ML2_MEGA_ONE_PASS");
-    for (int kw = 1; kw <= kMegaConsumerWarps; ++kw) {
-        const int passes = ceil_div(op.units, 32 * kw);
-        if (passes > (multi ? 4 : 1)) continue;
+    double best = -1.0;
+    for (int np = 1; np <= 2; ++np) {
+        const int kw = ceil_div(op.units, 32 * np);
+        if (kw > kMegaConsumerWarps) continue;
         const int groups = std::min(kMegaMaxGroups, kMegaConsumerWarps / kw);
-        // better: higher groups / passes; then fewer sweeps
-        const long lhs = (long)groups * op.passes, rhs = (long)op.groups * passes;
-        if (op.kw == 0 || lhs > rhs || (lhs == rhs && passes < op.passes)) {
+        const double score = (double)op.units / (kw * 32.0 * np) * (double)(groups * kw) / kMegaConsumerWarps;
+        if (score > best + 1e-9 || (score > best - 1e-9 && groups > op.groups)) {
+            best = std::max(best, score);
             op.kw = kw;
-            op.passes = passes;
+            op.np = np;
             op.groups = groups;
         }
     }
     if (op.kw == 0) return false;
+    // Rows of a full tile: whole batches for every group (a batch is 4 / np physical rows of a group), whole granules,
+    // at most kMegaGroupRows physical rows per group, and the tile has to fit the slot.
+    const int nruns = paired ? 2 : 1;
     auto a16 = [](int b) { return (b + 15) & ~15; };
-    op.woff_z = a16(op.run_rows * op.wsize * 4);
-    op.woff_s = op.woff_z + a16(op.run_rows * op.zsize * 4);
-    op.chunk_bytes = op.woff_s + a16(op.run_rows * op.ssize * 2);
+    auto tile_bytes = [&](int units) { return nruns * (units * op.wrow + a16(units * op.zrow) + a16(units * op.srow)); };
+    const int batch_units = std::max(1, (4 / op.np) / nruns);
+    int step = op.groups * batch_units;
+    step = step / std::__gcd(step, op.gran) * op.gran;
+    const int cap_units = op.groups * (kMegaGroupRows / nruns);
+    int rmax = 0;
+    for (int r = step; r <= cap_units && tile_bytes(r) <= slot_bytes; r += step) rmax = r;
+    if (rmax == 0) {
+        // a whole batch step does not fit: fall back to as many granules as do (groups then share a tile unevenly)
+        for (int r = op.gran; r <= cap_units && tile_bytes(r) <= slot_bytes; r += op.gran) rmax = r;
+    }
+    if (rmax == 0) return false;
+    op.rmax = rmax;
+    op.off_z = rmax * op.wrow;
+    op.off_s = op.off_z + a16(rmax * op.zrow);
+    op.run_bytes = op.off_s + a16(rmax * op.srow);
     return true;
 }
 
@@ -491,14 +506,13 @@ static int build_mega(Model* m)
     if (tp && !m->comm_attached) return ML2_OK;   // without peer memory the graph + NCCL path is used
     const ml2_config& c = m->cfg;
     const int dim = c.dim, hs = m->head_size;
-    if (m->heads_local > m->ctx->sm_count || (hs / 2) % 4 || m->tp > 8) return ML2_OK;
+    if (m->heads_local > m->ctx->sm_count || hs != kHeadMax || m->tp > 8) return ML2_OK;
+    if ((long long)std::max(c.vocab_size, std::max(c.hidden_dim, dim)) * (m->ctx->sm_count + 1) >= (1ll << 23)) return ML2_OK;   // tile arithmetic in exact floats
+    if (dim > 8 * kMegaNormVecs * kMegaConsThreads) return ML2_OK;   // a normalised input vector is held in registers by the CTA
     const CommLayout CL = comm_layout(m);
     auto peer = [&](int q, size_t off) { return static_cast<unsigned char*>(m->comm_peer[q]) + off; };
-    std::vector<MegaOp> ops;
     const size_t kv_layer = (size_t)c.seq_len * m->dim_local;
-    long long tiles_before = 0;
     // split attention: scratch for the exchange between the parts of a head, and the counters of their arrivals
-    bool split_ok = !getenv("ML2_NO_ATT_SPLIT");
     const int split = std::min(kMegaMaxSplit, m->ctx->sm_count / std::max(1, m->heads_local));
     if (!m->att_ml) {
         ML2_CUDA(cudaMalloc(&m->att_ml, (size_t)m->heads_local * kMegaMaxSplit * 2 * sizeof(float)));
@@ -510,130 +524,152 @@ static int build_mega(Model* m)
     }
     ML2_CUDA(cudaMemsetAsync(m->att_cnt, 0, (size_t)m->heads_local * sizeof(unsigned int), m->stream));
     m->att_seq = 0;
-    auto push = [&](MegaOp& op) {
-        op.rot = (int)(tiles_before % m->ctx->sm_count);
-        tiles_before += op.ntiles;
-        ops.push_back(op);
-    };
-    // residual stream: in place on one GPU; under tensor parallelism the update happens in the next norm
-    // operator's prologue and ping-pongs between two buffers (readers of the old one may still be running)
-    __half* x_cur = m->x;
-    __half* x_alt = tp ? reinterpret_cast<__half*>(peer(m->rank, CL.x2_off)) : nullptr;
-    int partial_ordinal = 0;
-    const float* pending_recv = nullptr;   // receive zone holding the partials not yet folded into x
-    auto norm_input = [&](MegaOp& op, const __half* gamma, bool first) {
-        op.gamma = gamma;
-        if (first) { op.pro = 2; op.in = x_cur; return; }
-        if (tp) {
-            op.pro = 3; op.tp = m->tp; op.in = x_cur; op.recv = pending_recv; op.x_next = x_alt;
-            std::swap(x_cur, x_alt);
-        } else {
-            op.pro = 1; op.in = x_cur;
-        }
-    };
-    auto partial_output = [&](MegaOp& op, int k_index) {
-        op.kind = MOP_PARTIAL;
-        op.tp = m->tp;
-        const size_t zone = (size_t)(partial_ordinal % CL.zones) * m->tp * dim * sizeof(float);
-        for (int q = 0; q < m->tp; ++q) {
-            op.peer_out[q] = reinterpret_cast<float*>(peer(q, CL.recv_off + zone + (size_t)m->rank * dim * sizeof(float)));
-            op.peer_done[q] = reinterpret_cast<unsigned int*>(peer(q, CL.done_off)) + k_index;
-        }
-        pending_recv = reinterpret_cast<const float*>(peer(m->rank, CL.recv_off + zone));
-        ++partial_ordinal;
-    };
-    for (int l = 0; l < c.n_layers; ++l) {
-        const LayerW& L = m->layers[l];
-        __half* kc = m->key_cache + (size_t)l * kv_layer;
-        __half* vc = m->value_cache + (size_t)l * kv_layer;
-        MegaOp q{};
-        q.kind = MOP_QKV; q.nmat = 3;
-        if (!mega_plan_op(q, 0, dim, m->dim_local, true)) return ML2_OK;
-        norm_input(q, L.rms_att, l == 0);
-        q.ntiles = 3 * (m->dim_local / 2 / q.rwc);
-        q.mat[0] = qwp(L.q); q.mat[1] = qwp(L.k); q.mat[2] = qwp(L.v);
-        q.out[0] = m->q; q.out[1] = kc; q.out[2] = vc;
-        push(q);
-        MegaOp a{};
-        a.kind = MOP_ATTN; a.tp = 1; a.in = m->q; a.out[0] = m->xb; a.kcache = kc; a.vcache = vc; a.ntiles = 0;
-        a.att_ml = m->att_ml; a.att_part = m->att_part; a.att_cnt = m->att_cnt; a.att_layer = l;
-        push(a);
-        MegaOp o{};
-        o.kind = MOP_RESID; o.pro = 0; o.nmat = 1;
-        if (!mega_plan_op(o, 0, m->dim_local, dim, false, true)) return ML2_OK;
-        o.ntiles = ceil_div(dim, o.run_rows);
-        o.mat[0] = qwp(L.o); o.out[0] = x_cur; o.in = m->xb;
-        if (o.passes > 1) split_ok = false;   // the multi-sweep prologue reads its input vector as stored
-        o.att_part = m->att_part;
-        if (tp) partial_output(o, (int)ops.size());
-        push(o);
-        MegaOp g{};
-        g.kind = MOP_SWIGLU; g.nmat = 2;
-        if (!mega_plan_op(g, 0, dim, m->hidden_local, true)) return ML2_OK;
-        norm_input(g, L.rms_ffn, false);
-        g.ntiles = ceil_div(m->hidden_local, g.rwc);
-        g.mat[0] = qwp(L.gate); g.mat[1] = qwp(L.up); g.out[0] = m->h;
-        push(g);
-        MegaOp d{};
-        d.kind = MOP_RESID; d.pro = 0; d.nmat = 1;
-        if (!mega_plan_op(d, 0, m->hidden_local, dim, false, true)) return ML2_OK;
-        d.ntiles = ceil_div(dim, d.run_rows);
-        d.mat[0] = qwp(L.down); d.out[0] = x_cur; d.in = m->h;
-        if (tp) partial_output(d, (int)ops.size());
-        push(d);
-    }
-    MegaOp cl{};
-    cl.kind = MOP_CLS; cl.nmat = 1;
-    if (!mega_plan_op(cl, 1, dim, m->vocab_local, false)) return ML2_OK;
-    norm_input(cl, m->rms_final, false);
-    cl.ntiles = ceil_div(m->vocab_local, cl.rwc);
-    cl.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
-    cl.out[0] = m->logits;
-    if (tp) {
-        cl.tp = m->tp;   // (norm_input set it already for the input side)
-        cl.out_row0 = m->vocab_row0;
-        for (int q = 0; q < m->tp; ++q) {
-            cl.peer_logits[q] = reinterpret_cast<__half*>(peer(q, CL.logits_off));
-            cl.peer_done[q] = reinterpret_cast<unsigned int*>(peer(q, CL.done_off)) + (int)ops.size();
-        }
-        m->logits_view = reinterpret_cast<__half*>(peer(m->rank, CL.logits_off));
-    } else {
-        m->logits_view = m->logits;
-    }
-    push(cl);
-    MegaOp am{};
-    am.kind = MOP_ARGMAX; am.ntiles = 0; am.tp = 1;
-    push(am);
 
-    m->att_split = (split_ok && split >= 2) ? split : 1;
-    if (const char* e = getenv("ML2_ATT_MIN_SEQ")) m->att_min_seq = atoi(e);
-    int slot = 0;
-    for (const MegaOp& op : ops)
-        if (op.ntiles > 0) slot = std::max(slot, op.nruns * op.chunk_bytes);
-    slot = (slot + 127) & ~127;
-    // scratch beside the ring: attention scores, or the staged input vector of a single-sweep operator, or the
-    // prepared-slice table of a multi-sweep operator (7 vectors of 16 bytes per lane slot)
-    int scratch = c.seq_len * 4;
-    for (const MegaOp& op : ops) {
-        if (op.ntiles == 0) continue;
-        scratch = std::max(scratch, op.passes > 1 ? op.kw * 32 * op.passes * kSliceVecs * 16 : op.rows * 2);
-    }
-    if (dim > 2 * 8 * kMegaConsumerWarps * 32) return ML2_OK;   // a normalised input vector is fetched as two pieces per thread
-    const int att_bytes = (scratch + 127) & ~127;
+    // The operator list for a ring slot of `slot_bytes`; false when some operator cannot be planned.
+    std::vector<MegaOp> ops;
+    auto plan_all = [&](int slot_bytes) -> bool {
+        ops.clear();
+        int rot = 0;
+        auto push = [&](MegaOp& op) {
+            op.rot = rot % m->ctx->sm_count;
+            rot += 37;   // the CTAs that own one granule more than the others change from operator to operator
+            op.seg_rot = m->ctx->sm_count / 3 + 1;
+            op.inv_ncta = 1.0f / (float)m->ctx->sm_count;
+            if (op.has_tiles) {
+                op.ngran = op.cols / op.gran;
+                op.gmax = op.rmax / op.gran;
+                op.inv_gmax = 1.0f / (float)op.gmax;
+            }
+            ops.push_back(op);
+        };
+        // residual stream: in place on one GPU; under tensor parallelism the update happens in the next norm
+        // operator's prologue and ping-pongs between two buffers (readers of the old one may still be running)
+        __half* x_cur = m->x;
+        __half* x_alt = tp ? reinterpret_cast<__half*>(peer(m->rank, CL.x2_off)) : nullptr;
+        int partial_ordinal = 0;
+        const float* pending_recv = nullptr;   // receive zone holding the partials not yet folded into x
+        auto norm_input = [&](MegaOp& op, const __half* gamma, bool first) {
+            op.gamma = gamma;
+            if (first) { op.pro = 2; op.in = x_cur; return; }
+            if (tp) {
+                op.pro = 3; op.tp = m->tp; op.in = x_cur; op.recv = pending_recv; op.x_next = x_alt;
+                std::swap(x_cur, x_alt);
+            } else {
+                op.pro = 1; op.in = x_cur;
+            }
+        };
+        auto partial_output = [&](MegaOp& op, int k_index) {
+            op.kind = MOP_PARTIAL;
+            op.tp = m->tp;
+            const size_t zone = (size_t)(partial_ordinal % CL.zones) * m->tp * dim * sizeof(float);
+            for (int q = 0; q < m->tp; ++q) {
+                op.peer_out[q] = reinterpret_cast<float*>(peer(q, CL.recv_off + zone + (size_t)m->rank * dim * sizeof(float)));
+                op.peer_done[q] = reinterpret_cast<unsigned int*>(peer(q, CL.done_off)) + k_index;
+            }
+            pending_recv = reinterpret_cast<const float*>(peer(m->rank, CL.recv_off + zone));
+            ++partial_ordinal;
+        };
+        for (int l = 0; l < c.n_layers; ++l) {
+            const LayerW& L = m->layers[l];
+            __half* kc = m->key_cache + (size_t)l * kv_layer;
+            __half* vc = m->value_cache + (size_t)l * kv_layer;
+            MegaOp q{};
+            q.kind = MOP_QKV;
+            if (!mega_plan_op(q, 0, dim, m->dim_local, 3, false, slot_bytes)) return false;
+            norm_input(q, L.rms_att, l == 0);
+            q.mat[0] = qwp(L.q); q.mat[1] = qwp(L.k); q.mat[2] = qwp(L.v);
+            q.out[0] = m->q; q.out[1] = kc; q.out[2] = vc;
+            push(q);
+            MegaOp a{};
+            a.kind = MOP_ATTN; a.tp = 1; a.in = m->q; a.out[0] = m->xb; a.kcache = kc; a.vcache = vc;
+            a.att_ml = m->att_ml; a.att_part = m->att_part; a.att_cnt = m->att_cnt; a.att_layer = l;
+            push(a);
+            MegaOp o{};
+            o.kind = MOP_RESID; o.pro = 0;
+            if (!mega_plan_op(o, 0, m->dim_local, dim, 1, false, slot_bytes)) return false;
+            o.mat[0] = qwp(L.o); o.out[0] = x_cur; o.in = m->xb;
+            o.att_part = m->att_part;   // input of the split attention path: partial outputs summed in the prologue
+            if (tp) partial_output(o, (int)ops.size());
+            push(o);
+            MegaOp g{};
+            g.kind = MOP_SWIGLU;
+            if (!mega_plan_op(g, 0, dim, m->hidden_local, 2, true, slot_bytes)) return false;
+            norm_input(g, L.rms_ffn, false);
+            g.mat[0] = qwp(L.gate); g.mat[1] = qwp(L.up); g.out[0] = m->h;
+            push(g);
+            MegaOp d{};
+            d.kind = MOP_RESID; d.pro = 0;
+            if (!mega_plan_op(d, 0, m->hidden_local, dim, 1, false, slot_bytes)) return false;
+            d.mat[0] = qwp(L.down); d.out[0] = x_cur; d.in = m->h;
+            if (tp) partial_output(d, (int)ops.size());
+            push(d);
+        }
+        MegaOp cl{};
+        cl.kind = MOP_CLS;
+        if (!mega_plan_op(cl, 1, dim, m->vocab_local, 1, false, slot_bytes)) return false;
+        norm_input(cl, m->rms_final, false);
+        cl.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
+        cl.out[0] = m->logits;
+        if (tp) {
+            cl.tp = m->tp;   // (norm_input set it already for the input side)
+            cl.out_row0 = m->vocab_row0;
+            for (int q = 0; q < m->tp; ++q) {
+                cl.peer_logits[q] = reinterpret_cast<__half*>(peer(q, CL.logits_off));
+                cl.peer_done[q] = reinterpret_cast<unsigned int*>(peer(q, CL.done_off)) + (int)ops.size();
+            }
+            m->logits_view = reinterpret_cast<__half*>(peer(m->rank, CL.logits_off));
+        } else {
+            m->logits_view = m->logits;
+        }
+        push(cl);
+        MegaOp am{};
+        am.kind = MOP_ARGMAX; am.tp = 1;
+        push(am);
+        return true;
+    };
+
     // everything the opt-in limit of one CTA leaves after the kernel's static shared memory (1 KB kept spare)
     int optin = 0;
     ML2_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->ctx->device));
     cudaFuncAttributes fa{};
     ML2_CUDA(cudaFuncGetAttributes(&fa, decode_token_kernel<true>));
-    int budget = optin - (int)fa.sharedSizeBytes - 1024;
-    if (const char* e = getenv("ML2_MEGA_SMEM_KB")) budget = std::min(budget, atoi(e) * 1024);
-    int nstage = (budget - att_bytes) / slot;
-    if (nstage > kMegaMaxStages) nstage = kMegaMaxStages;
-    if (nstage < 2) return ML2_OK;
+    const int budget = optin - (int)fa.sharedSizeBytes - 1024;
+    if (!plan_all(budget)) return ML2_OK;   // lane mappings do not depend on the slot size
+    // scratch beside the ring: the prepared input table of a weight operator, or the attention's scores and partial outputs
+    int scratch = c.seq_len * 4 + kMegaConsumerWarps * kHeadMax * 4;
+    for (const MegaOp& op : ops) {
+        if (!op.has_tiles) continue;
+        const int tab_n = op.kw * 32 * op.np;
+        scratch = std::max(scratch, op.fmt == 0 ? tab_n * 5 * 16 : tab_n * 16);
+        if (op.pro != 0 && (op.fmt == 0 ? tab_n * 4 : tab_n) > kMegaNormVecs * kMegaConsThreads) return ML2_OK;
+    }
+    scratch = (scratch + 127) & ~127;
+    int nstage = 0, slot = 0;
+    for (int ns = 4; ns >= 2 && !nstage; --ns) {
+        const int sb = ((budget - scratch) / ns) & ~127;
+        if (sb < 1024 || !plan_all(sb)) continue;
+        // the slot needs no more than the largest tile
+        int need = 0;
+        for (const MegaOp& op : ops)
+            if (op.has_tiles) need = std::max(need, (op.paired ? 2 : 1) * op.run_bytes);
+        nstage = ns;
+        slot = std::min(sb, (need + 127) & ~127);
+    }
+    if (!nstage) return ML2_OK;
+    // every array a tile is copied from must be 16-byte aligned (the rows of a tile start at a whole granule)
+    for (const MegaOp& op : ops) {
+        if (!op.has_tiles) continue;
+        for (int q = 0; q < op.nmat; ++q) {
+            const uintptr_t bits = reinterpret_cast<uintptr_t>(op.mat[q].w) | reinterpret_cast<uintptr_t>(op.mat[q].z) |
+                                   reinterpret_cast<uintptr_t>(op.mat[q].s);
+            if (bits & 15u) return ML2_OK;
+        }
+    }
+    m->att_split = split >= 2 ? split : 1;
     m->mega_slot = slot;
     m->mega_nstage = nstage;
-    m->mega_att_bytes = att_bytes;
-    m->mega_smem = nstage * slot + att_bytes;
+    m->mega_att_bytes = scratch;
+    m->mega_smem = nstage * slot + scratch;
     m->mega_nops = (int)ops.size();
     m->mega_grid = m->ctx->sm_count;
     ML2_CUDA(cudaFuncSetAttribute(decode_token_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->mega_smem));
@@ -653,7 +689,7 @@ static int build_mega(Model* m)
         m->mega_seq = 0;
     }
     ML2_CUDA(cudaStreamSynchronize(m->stream));
-    if (getenv("ML2_MEGA_PROF") && !m->mega_prof) {
+    if (m->want_prof && !m->mega_prof) {
         ML2_CUDA(cudaMalloc(&m->mega_prof, (size_t)m->mega_grid * 64 * sizeof(long long)));
         ML2_CUDA(cudaMemset(m->mega_prof, 0, (size_t)m->mega_grid * 64 * sizeof(long long)));
     }
@@ -683,7 +719,7 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     prm.n_layers = m->cfg.n_layers;
     prm.att_split = (m->att_split > 1 && pos + 1 >= m->att_min_seq) ? m->att_split : 1;
     prm.att_seq = prm.att_split > 1 ? ++m->att_seq : m->att_seq;
-    { const char* d = getenv("ML2_MEGA_DEBUG"); prm.debug = d ? atoi(d) : 0; }
+    prm.wait_cycles = m->ctx->wait_cycles;
     void* args[] = {&prm};
     const void* fn = m->mega_prof ? (const void*)decode_token_kernel<true> : (const void*)decode_token_kernel<false>;
     ML2_CUDA(cudaLaunchCooperativeKernel(fn, dim3(m->mega_grid), dim3(kMegaThreads), args, (size_t)m->mega_smem, m->stream));
@@ -758,6 +794,8 @@ int ml2_model_create(ml2_ctx* h, const ml2_config* cfg, int tp_size, int tp_rank
     m->use_mega = !(em && *em == '1');
     const char* ep = getenv("ML2_NO_PDL");
     m->use_pdl = !(ep && *ep == '1');
+    const char* epf = getenv("ML2_MEGA_PROF");
+    m->want_prof = epf && *epf == '1';
     ML2_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     ctx->stream = m->stream;
     int rc;

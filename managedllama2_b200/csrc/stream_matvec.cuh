@@ -124,21 +124,29 @@ __device__ __forceinline__ void transpose_reduce(float (&v)[RW], int lane)
 //   b = (w & 0x00f000f0) | 0x64006400   halves = fp16(1024 + 16*n1), fp16(1024 + 16*n5)    -> mixed FMAs with x1, x5 (acc B)
 //   c, d: the same on w >> 8 (n2, n6 and n3, n7).
 // The constant offsets (1024 * sum of the inputs) are removed by the accumulators' initial values; B carries a factor 16.
-// (Reading the pair register as one fp32 to skip the high-half extraction was tried: eight more registers for the
-// fp32 copies of x4 / x6 cost more in this register-bound loop than the two integer-pipe instructions saved.)
+// The mixed FMA reads either half of a register at no cost (no extraction instruction is issued).
 struct XSlice {
     uint32_t xp[16];   // fp16 pairs for the mixed FMAs
     float a0, b0;      // accumulator start values: -1024 * S(even inputs), -1024 * S(odd inputs)
     float c1;          // sum of all 32 inputs (zero-point term)
 };
 
+// (w & mask) | bits as ONE three-input logic instruction. Written as `(w & mask) | bits` in C++ the compiler emits an AND
+// and an OR (measured: 9 instead of 5 integer-pipe instructions per packed word, and that pipe bounds this loop).
+__device__ __forceinline__ uint32_t and_or(uint32_t w, uint32_t mask, uint32_t bits)
+{
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(d) : "r"(w), "r"(mask), "r"(bits));
+    return d;
+}
+
 __device__ __forceinline__ void word_dot(uint32_t w, const uint32_t* xp, float& A, float& B, float& D)
 {
-    const uint32_t a = (w & 0x000f000fu) | 0x64006400u;
-    const uint32_t b = (w & 0x00f000f0u) | 0x64006400u;
+    const uint32_t a = and_or(w, 0x000f000fu, 0x64006400u);
+    const uint32_t b = and_or(w, 0x00f000f0u, 0x64006400u);
     const uint32_t w8 = w >> 8;
-    const uint32_t c = (w8 & 0x000f000fu) | 0x64006400u;
-    const uint32_t d = (w8 & 0x00f000f0u) | 0x64006400u;
+    const uint32_t c = and_or(w8, 0x000f000fu, 0x64006400u);
+    const uint32_t d = and_or(w8, 0x00f000f0u, 0x64006400u);
     A = fma_f16_f32(lo16(a), lo16(xp[0]), A);
     D = fma_f16_f32(hi16(a), hi16(xp[0]), D);
     B = fma_f16_f32(lo16(b), lo16(xp[1]), B);
