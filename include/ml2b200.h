@@ -11,8 +11,11 @@
  *     Each C# subclass body becomes a single P/Invoke.
  *
  *  2. Model level: the per-token operator sequence of `Transformer.Forward`
- *     (src/Transformer.cs:158-190) as five fused kernels per layer inside one CUDA graph, with
- *     optional tensor parallelism (one process per GPU, NCCL).
+ *     (src/Transformer.cs:158-190) as ONE persistent kernel launch per token (one CTA per SM; the
+ *     operators hand over through device-wide counters, weights stream through a shared-memory ring
+ *     across operator boundaries), with optional tensor parallelism: one process per GPU, the sum of
+ *     the row-sharded mat-vecs fused into that kernel over peer memory. A CUDA graph of five fused
+ *     kernels per layer (with NCCL all-reduces under tensor parallelism) is the alternative path.
  *
  * Every function returns 0 on success or a negative ML2_E_* code; `ml2_last_error()` gives the text
  * for the calling thread. Nothing throws, nothing traps the device, no call falls back to the CPU.
@@ -69,6 +72,11 @@ int ml2_ctx_set_stream(ml2_ctx* ctx, void* cuda_stream);
  * the reference's semantics are plain stream order). */
 int ml2_ctx_set_pdl(ml2_ctx* ctx, int enabled);
 int ml2_ctx_synchronize(ml2_ctx* ctx);
+/* Budget of every device-side wait (mbarrier phases, operator counters, peer counters), in SM clock
+ * cycles; default 4e9 (about two seconds). A wait that runs out writes the error word and the kernel
+ * runs to its end; the next synchronising call returns ML2_E_DEVICE. No counterpart in the reference
+ * (its kernels never wait on one another). */
+int ml2_ctx_set_wait_limit(ml2_ctx* ctx, long long sm_cycles);
 /* Reads and clears the device error word written when a kernel's bounded wait expired. */
 int ml2_ctx_status(ml2_ctx* ctx, unsigned* error, unsigned* detail);
 /* Number of kernels this library has launched through `ctx` so far. */
@@ -192,9 +200,17 @@ int ml2_model_bind_runstate(ml2_model* model, const ml2_runstate* rs);
 int ml2_model_runstate(ml2_model* model, ml2_runstate* rs);
 /* Transformer.Forward(position, nextPosition) followed by the greedy Sampler.Sample
  * (src/Transformer.cs:158-190, src/Sampler.cs:44-47): asynchronous; tokens[next_pos] is written on the
- * device when write_token != 0. One CUDA-graph replay per call. */
+ * device when write_token != 0. One persistent-kernel launch (or one CUDA-graph replay) per call. Refused with
+ * ML2_E_STATE after a kernel's bounded wait ran out, until ml2_model_reset. */
 int ml2_model_forward(ml2_model* model, int pos, int next_pos, int write_token);
+/* Waits for the model's stream and reads the device error word: ML2_E_DEVICE if a bounded wait ran out (as do
+ * ml2_model_step_host, ml2_model_read_token, ml2_model_read_logits and ml2_model_generate, whose device-to-host
+ * read carries the error word along). */
 int ml2_model_synchronize(ml2_model* model);
+/* After ML2_E_DEVICE: clears the error word and brings every counter the persistent kernel keeps between tokens
+ * back to its start. Under tensor parallelism every rank calls it before any rank runs its next forward. No
+ * counterpart in the reference (its kernels never wait on one another). */
+int ml2_model_reset(ml2_model* model);
 long long ml2_model_launches_per_token(ml2_model* model);
 int ml2_model_set_tokens(ml2_model* model, const int* tokens_host, int first, int count);
 /* Stream-ordered 4-byte host->device copy of one token id; `token_pinned_host` must stay valid until it ran. */
@@ -216,9 +232,17 @@ int ml2_model_read_logits(ml2_model* model, void* logits_host_f16);
 int ml2_model_comm_handle(ml2_model* model, void* out64);
 int ml2_model_comm_attach(ml2_model* model, const void* handles_rank_order, int n_ranks);
 /* Diagnostics: per-CTA cycle counters of the last persistent-kernel launch, 64 values per CTA ([0..5] total,
- * dependency waits, ring waits, partial-slot waits, attention, prologue; [8..31] wait / prologue / tile cycles per
- * operator kind; [32..43] producer and finalizer busy and wait cycles); needs ML2_MEGA_PROF=1 in the environment. */
+ * dependency waits, ring waits, cycles inside the arithmetic batches, attention, prologue; [8..31] wait / prologue /
+ * tile cycles per operator kind; [32..35] copy warp and tail warp total and wait cycles); needs ML2_MEGA_PROF=1 in
+ * the environment when the model is created. */
 int ml2_model_debug_prof(ml2_model* model, long long* out, int n);
+/* Diagnostics (failure-path test): makes the model expect one more round of operator arrivals than its counters
+ * hold, as after a rank skipped a forward; the next forward's waits then run out after the wait limit, the kernel
+ * returns, and the synchronising call reports ML2_E_DEVICE. Touches nothing on the device. */
+int ml2_model_debug_skip_launch(ml2_model* model);
+/* Tuning: the sequence length from which the persistent kernel splits every head's attention over several CTAs
+ * (default 704, the measured crossover on a B200 for the 13B shape; shorter sequences keep one CTA per head). */
+int ml2_model_set_split_attention_from(ml2_model* model, int min_seq);
 /* The CUDA stream the model launches on (for events or for ordering other work after it). */
 int ml2_model_stream(ml2_model* model, void** cuda_stream);
 /* Times each kernel kind alone over all layers (kinds: 0 qkv, 1 attention, 2 o-proj, 3 gate/up, 4 down,

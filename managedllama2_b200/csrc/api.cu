@@ -24,10 +24,13 @@ int fail(int code, const char* fmt, ...)
     return code;
 }
 
-static int env_int(const char* name, int dflt)
+int use_device(const Ctx* ctx)
 {
-    const char* v = getenv(name);
-    return (v && *v) ? atoi(v) : dflt;
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e == cudaSuccess && cur != ctx->device) e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return fail(ML2_E_CUDA, "cudaSetDevice(%d): %s", ctx->device, cudaGetErrorString(e));
+    return ML2_OK;
 }
 
 // ---- launch planning for the streaming mat-vec ---------------------------------------------------
@@ -58,13 +61,10 @@ int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, 
     p.rw = 4;
     if (fmt == Fmt::Int4 && (p.ssize & 1)) p.rw = 8;
     if (paired && p.rw != 4) p.rw = 4;  // paired chunks are 4 rows; ragged scale runs take the slow copy path
-    p.rw = env_int("ML2_MV_RW", p.rw);
-    if (p.rw != 4 && p.rw != 8) return fail(ML2_E_INVALID, "ML2_MV_RW must be 4 or 8");
 
     // chunks per stage: aim at >= 8 consumer warps per CTA
     int mw = paired ? 2 : 1;
     while (p.kw * mw < 8 && mw * p.rw < 16) mw += paired ? 2 : 1;
-    mw = env_int("ML2_MV_MW", mw);
     if (mw < 1 || mw * p.rw > kMaxR || (paired && (mw & 1)) || (p.kw * mw + 2) * 32 > 1024)
         return fail(ML2_E_INVALID, "mat-vec plan: mw=%d invalid for kw=%d rw=%d", mw, p.kw, p.rw);
     p.mw = mw;
@@ -75,16 +75,15 @@ int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, 
     p.chunk_bytes = p.woff_s + a16(p.rw * p.ssize * 2);
     const int stage_bytes = p.chunk_bytes * p.mw;
 
-    const int smem_budget = env_int("ML2_MV_SMEM_KB", 96) * 1024;
-    int ctas = env_int("ML2_MV_CTAS", 0);
+    const int smem_budget = 96 * 1024;
+    int ctas = 0;
     const int threads = (p.kw * p.mw + 2) * 32;  // consumers + producer + finalizer
     if (ctas <= 0) {
         ctas = 1;
         // small CTAs: co-schedule several per SM while the ring of each keeps >= 3 stages
         while (ctas < 4 && (ctas + 1) * threads <= 640 && (ctas + 1) * 3 * stage_bytes <= smem_budget) ++ctas;
     }
-    int nstage = env_int("ML2_MV_STAGES", 0);
-    if (nstage <= 0) nstage = smem_budget / ctas / stage_bytes;
+    int nstage = smem_budget / ctas / stage_bytes;
     if (nstage > 8) nstage = 8;
     if (nstage < 2) nstage = 2;
     p.nstage = nstage;
@@ -120,24 +119,21 @@ static cudaError_t launch_rw(const Ctx* ctx, const MatVecPlan& pl, const MatVecP
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
     // the opt-in to large dynamic shared memory is per function and per device: once is enough
-    static bool attr_done[2][16] = {};
+    static bool attr_done[2][2][16] = {};
     const int dev = ctx->device & 15;
-    if (pl.rw == 4) {
-        auto k = stream_matvec_kernel<F, E, P, 4>;
-        if (!attr_done[0][dev]) {
-            e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (e != cudaSuccess) return e;
-            attr_done[0][dev] = true;
-        }
-        return cudaLaunchKernelEx(&cfg, k, prm);
-    }
-    auto k = stream_matvec_kernel<F, E, P, 8>;
-    if (!attr_done[1][dev]) {
+    const int big = pl.threads > 512 ? 1 : 0, r8 = pl.rw == 4 ? 0 : 1;
+    const void* k = nullptr;
+    if (!big && !r8) k = (const void*)stream_matvec_kernel<F, E, P, 4, 512>;
+    if (!big && r8) k = (const void*)stream_matvec_kernel<F, E, P, 8, 512>;
+    if (big && !r8) k = (const void*)stream_matvec_kernel<F, E, P, 4, 1024>;
+    if (big && r8) k = (const void*)stream_matvec_kernel<F, E, P, 8, 1024>;
+    if (!attr_done[big][r8][dev]) {
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        attr_done[1][dev] = true;
+        attr_done[big][r8][dev] = true;
     }
-    return cudaLaunchKernelEx(&cfg, k, prm);
+    void* args[] = {const_cast<MatVecParams*>(&prm)};
+    return cudaLaunchKernelExC(&cfg, k, args);
 }
 
 int launch_matvec(Ctx* ctx, Fmt fmt, Epi epi, Pro pro, const MatVecPlan& pl, MatVecParams prm, bool pdl)
@@ -146,7 +142,7 @@ int launch_matvec(Ctx* ctx, Fmt fmt, Epi epi, Pro pro, const MatVecPlan& pl, Mat
     prm.kw = pl.kw; prm.mw = pl.mw; prm.nstage = pl.nstage; prm.chunk_bytes = pl.chunk_bytes;
     prm.woff_z = pl.woff_z; prm.woff_s = pl.woff_s; prm.ntiles = pl.ntiles;
     prm.status = ctx->status_dev;
-    prm.debug = env_int("ML2_MV_DEBUG", 0);
+    if (int rc = use_device(ctx)) return rc;
     cudaError_t e = cudaErrorInvalidValue;
 #define ML2_CASE(F_, E_, P_) \
     if (fmt == F_ && epi == E_ && pro == P_) e = launch_rw<F_, E_, P_>(ctx, pl, prm, pdl);
@@ -186,6 +182,7 @@ static int check_cuda(const char* what)
 template <typename... Args>
 static int launch_small(Ctx* ctx, const char* what, void (*kernel)(Args...), dim3 grid, dim3 block, Args... args)
 {
+    if (int rc = use_device(ctx)) return rc;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -258,9 +255,17 @@ int ml2_ctx_set_pdl(ml2_ctx* h, int on)
     reinterpret_cast<Ctx*>(h)->pdl = on != 0;
     return ML2_OK;
 }
+int ml2_ctx_set_wait_limit(ml2_ctx* h, long long sm_cycles)
+{
+    if (!h) return fail(ML2_E_INVALID, "null context");
+    if (sm_cycles < 1000) return fail(ML2_E_INVALID, "wait limit of %lld cycles is too short", sm_cycles);
+    reinterpret_cast<Ctx*>(h)->wait_cycles = sm_cycles;
+    return ML2_OK;
+}
 int ml2_ctx_synchronize(ml2_ctx* h)
 {
     if (!h) return fail(ML2_E_INVALID, "null context");
+    if (int rc = use_device(reinterpret_cast<Ctx*>(h))) return rc;
     const cudaError_t e = cudaStreamSynchronize(reinterpret_cast<Ctx*>(h)->stream);
     if (e != cudaSuccess) return fail(ML2_E_CUDA, "synchronize: %s", cudaGetErrorString(e));
     return ML2_OK;
@@ -269,6 +274,7 @@ int ml2_ctx_status(ml2_ctx* h, unsigned* error, unsigned* detail)
 {
     Ctx* c = reinterpret_cast<Ctx*>(h);
     if (!c) return fail(ML2_E_INVALID, "null context");
+    if (int rc = use_device(c)) return rc;
     DeviceStatus st{};
     cudaError_t e = cudaMemcpyAsync(&st, c->status_dev, sizeof(st), cudaMemcpyDeviceToHost, c->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);

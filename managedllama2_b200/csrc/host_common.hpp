@@ -35,6 +35,9 @@ enum class Pro : int;
 struct MatVecParams;
 
 int fail(int code, const char* fmt, ...);
+// Makes the context's device current for the calling thread (every entry point does this first: a thread may hold
+// several contexts, or may have switched device in between).
+int use_device(const Ctx* ctx);
 int plan_matvec(const Ctx* ctx, Fmt fmt, Epi epi, int rows, int cols, int nmat, MatVecPlan* pl);
 int launch_matvec(Ctx* ctx, Fmt fmt, Epi epi, Pro pro, const MatVecPlan& pl, MatVecParams prm, bool pdl);
 

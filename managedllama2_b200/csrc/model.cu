@@ -178,7 +178,9 @@ struct Model {
     int mega_nops = 0, mega_nstage = 0, mega_slot = 0, mega_att_bytes = 0, mega_smem = 0, mega_grid = 0;
     unsigned int mega_seq = 0;
     long long* mega_prof = nullptr;
-    bool want_prof = false;                 // cycle counters of the diagnostic instantiation (ML2_MEGA_PROF=1 at model creation)
+    bool want_prof = false;
+    bool poisoned = false;                  // a kernel's wait ran out: counters are mid-token, forwards are refused until ml2_model_reset
+    int last_pos = 0;                       // position of the latest forward (ml2_model_profile times the attention there)                 // cycle counters of the diagnostic instantiation (ML2_MEGA_PROF=1 at model creation)
     unsigned int* mega_done_ptr = nullptr;
     __half* logits_view = nullptr;          // where the full logits of the persistent kernel land
     int* sample_indices = nullptr;          // token ids carried through the sampler's sort (RunState.indices)
@@ -728,6 +730,20 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     return ML2_OK;
 }
 
+// Reads the device error word together with whatever the caller just synchronised on. A kernel whose bounded wait ran
+// out leaves garbage behind and the monotonic counters mid-token: the model refuses further forwards until it is reset.
+static int check_device_status(Model* m)
+{
+    DeviceStatus st{};
+    ML2_CUDA(cudaMemcpyAsync(&st, m->ctx->status_dev, sizeof(st), cudaMemcpyDeviceToHost, m->stream));
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    if (st.error) {
+        m->poisoned = true;
+        return fail(ML2_E_DEVICE, "a kernel gave up waiting (code %u, operator %u); call ml2_model_reset before the next forward", st.error, st.detail);
+    }
+    return ML2_OK;
+}
+
 static int check_bound(Model* m)
 {
     if (!m->embed || !m->classifier || !m->rms_final) return fail(ML2_E_STATE, "model: globals are not bound");
@@ -796,27 +812,40 @@ int ml2_model_create(ml2_ctx* h, const ml2_config* cfg, int tp_size, int tp_rank
     m->use_pdl = !(ep && *ep == '1');
     const char* epf = getenv("ML2_MEGA_PROF");
     m->want_prof = epf && *epf == '1';
-    ML2_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
-    ctx->stream = m->stream;
-    int rc;
-    if ((rc = dev_alloc(m, (void**)&m->step, sizeof(StepState)))) return rc;
-    if ((rc = dev_alloc(m, (void**)&m->rope_table, (size_t)c.seq_len * (hs / 2) * sizeof(float2)))) return rc;
-    rope_table_kernel<<<ceil_div(c.seq_len * (hs / 2), 256), 256, 0, m->stream>>>(m->rope_table, c.seq_len, hs, c.rope_theta);
-    ++ctx->launches;
-    if (tp_size > 1) {
-        if ((rc = dev_alloc(m, (void**)&m->partial, (size_t)c.dim * sizeof(float)))) return rc;
-        if ((rc = dev_alloc(m, (void**)&m->logits_local, (size_t)m->vocab_local * sizeof(__half)))) return rc;
-        {   // peer-visible buffer of the persistent kernel (counters, receive zones, logits, second residual buffer)
-            const CommLayout CL = comm_layout(m);
-            ML2_CUDA(cudaMalloc(&m->comm_local, CL.total));
-            ML2_CUDA(cudaMemsetAsync(m->comm_local, 0, CL.total, m->stream));
+    cudaStream_t caller_stream = ctx->stream;
+    // everything below may fail half way: one exit that frees what was made and gives the caller's stream back
+    auto build = [&]() -> int {
+        ML2_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+        ctx->stream = m->stream;
+        int rc;
+        if ((rc = dev_alloc(m, (void**)&m->step, sizeof(StepState)))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->rope_table, (size_t)c.seq_len * (hs / 2) * sizeof(float2)))) return rc;
+        rope_table_kernel<<<ceil_div(c.seq_len * (hs / 2), 256), 256, 0, m->stream>>>(m->rope_table, c.seq_len, hs, c.rope_theta);
+        ++ctx->launches;
+        if (tp_size > 1) {
+            if ((rc = dev_alloc(m, (void**)&m->partial, (size_t)c.dim * sizeof(float)))) return rc;
+            if ((rc = dev_alloc(m, (void**)&m->logits_local, (size_t)m->vocab_local * sizeof(__half)))) return rc;
+            {   // peer-visible buffer of the persistent kernel (counters, receive zones, logits, second residual buffer)
+                const CommLayout CL = comm_layout(m);
+                ML2_CUDA(cudaMalloc(&m->comm_local, CL.total));
+                ML2_CUDA(cudaMemsetAsync(m->comm_local, 0, CL.total, m->stream));
+            }
+            if ((rc = nccl_load())) return rc;
+            ncclUniqueId id;
+            memcpy(&id, nccl_id128, sizeof(id));
+            ML2_NCCL(g_nccl.CommInitRank(&m->comm, tp_size, id, tp_rank));
         }
-        if ((rc = nccl_load())) return rc;
-        ncclUniqueId id;
-        memcpy(&id, nccl_id128, sizeof(id));
-        ML2_NCCL(g_nccl.CommInitRank(&m->comm, tp_size, id, tp_rank));
+        ML2_CUDA(cudaStreamSynchronize(m->stream));
+        return ML2_OK;
+    };
+    const int rc = build();
+    if (rc) {
+        char keep[512];
+        snprintf(keep, sizeof(keep), "%s", ml2_last_error());
+        ml2_model_destroy(reinterpret_cast<ml2_model*>(m));
+        ctx->stream = caller_stream;
+        return fail(rc, "%s", keep);
     }
-    ML2_CUDA(cudaStreamSynchronize(m->stream));
     *out = reinterpret_cast<ml2_model*>(m);
     return ML2_OK;
 }
@@ -837,7 +866,7 @@ int ml2_model_destroy(ml2_model* h)
     Model* m = reinterpret_cast<Model*>(h);
     if (!m) return ML2_OK;
     cudaSetDevice(m->ctx->device);
-    cudaStreamSynchronize(m->stream);
+    if (m->stream) cudaStreamSynchronize(m->stream);
     if (m->exec) cudaGraphExecDestroy(m->exec);
     if (m->graph) cudaGraphDestroy(m->graph);
     if (m->comm) g_nccl.CommDestroy(m->comm);
@@ -848,7 +877,7 @@ int ml2_model_destroy(ml2_model* h)
     if (m->mega_done) cudaFree(m->mega_done);
     for (void* p : m->owned) cudaFree(p);
     if (m->ctx->stream == m->stream) m->ctx->stream = nullptr;
-    cudaStreamDestroy(m->stream);
+    if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
     return ML2_OK;
 }
@@ -955,7 +984,10 @@ int ml2_model_forward(ml2_model* h, int pos, int next_pos, int write_token)
     if (pos < 0 || pos >= m->cfg.seq_len || next_pos < 0 || next_pos > m->cfg.seq_len)
         return fail(ML2_E_INVALID, "forward: pos=%d next_pos=%d outside [0,%d)", pos, next_pos, m->cfg.seq_len);
     Ctx* ctx = m->ctx;
+    if ((rc = use_device(ctx))) return rc;
+    if (m->poisoned) return fail(ML2_E_STATE, "forward: an earlier kernel gave up waiting; call ml2_model_reset first");
     ctx->stream = m->stream;
+    m->last_pos = pos;
     if (!m->mega_built && (rc = build_mega(m))) return rc;
     if (m->mega_ok) return forward_mega(m, pos, next_pos, write_token);
     if (!m->use_graph) return enqueue_token(m, pos, next_pos, write_token);
@@ -1007,7 +1039,35 @@ int ml2_model_synchronize(ml2_model* h)
 {
     Model* m = reinterpret_cast<Model*>(h);
     if (!m) return fail(ML2_E_INVALID, "null model");
+    if (int rc = use_device(m->ctx)) return rc;
+    return check_device_status(m);
+}
+
+int ml2_model_reset(ml2_model* h)
+{
+    // After ML2_E_DEVICE: waits for whatever is still running, clears the error word and brings every counter the
+    // persistent kernel keeps between tokens back to its start (operator arrivals, split-attention arrivals, launch
+    // numbers). Under tensor parallelism every rank must call it before any rank runs the next forward: the receive
+    // zones and counters of a rank are written by its peers.
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    if (int rc = use_device(m->ctx)) return rc;
     ML2_CUDA(cudaStreamSynchronize(m->stream));
+    ML2_CUDA(cudaMemsetAsync(m->ctx->status_dev, 0, sizeof(DeviceStatus), m->stream));
+    if (m->mega_done_ptr && m->mega_nops > 0) ML2_CUDA(cudaMemsetAsync(m->mega_done_ptr, 0, (size_t)m->mega_nops * sizeof(unsigned int), m->stream));
+    if (m->att_cnt) ML2_CUDA(cudaMemsetAsync(m->att_cnt, 0, (size_t)m->heads_local * sizeof(unsigned int), m->stream));
+    m->mega_seq = 0;
+    m->att_seq = 0;
+    ML2_CUDA(cudaStreamSynchronize(m->stream));
+    m->poisoned = false;
+    return ML2_OK;
+}
+
+static int check_token_ids(const Model* m, const int* ids, int count, const char* what)
+{
+    for (int i = 0; i < count; ++i)
+        if (ids[i] < 0 || ids[i] >= m->cfg.vocab_size)
+            return fail(ML2_E_INVALID, "%s: token id %d at index %d is outside the vocabulary [0, %d)", what, ids[i], i, m->cfg.vocab_size);
     return ML2_OK;
 }
 
@@ -1017,6 +1077,8 @@ int ml2_model_set_tokens(ml2_model* h, const int* tokens_host, int first, int co
     if (!m || !tokens_host) return fail(ML2_E_INVALID, "set_tokens: null argument");
     if (!m->tokens) return fail(ML2_E_STATE, "set_tokens: run state missing");
     if (first < 0 || count < 0 || first + count > m->cfg.seq_len + 1) return fail(ML2_E_INVALID, "set_tokens: range");
+    if (int rc = check_token_ids(m, tokens_host, count, "set_tokens")) return rc;
+    if (int rc = use_device(m->ctx)) return rc;
     ML2_CUDA(cudaMemcpyAsync(m->tokens + first, tokens_host, (size_t)count * sizeof(int), cudaMemcpyHostToDevice, m->stream));
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     return ML2_OK;
@@ -1028,6 +1090,8 @@ int ml2_model_put_token_async(ml2_model* h, int pos, const int* token_pinned_hos
     if (!m || !token_pinned_host) return fail(ML2_E_INVALID, "put_token_async: null argument");
     if (!m->tokens) return fail(ML2_E_STATE, "put_token_async: run state missing");
     if (pos < 0 || pos > m->cfg.seq_len) return fail(ML2_E_INVALID, "put_token_async: pos");
+    if (int rc = check_token_ids(m, token_pinned_host, 1, "put_token_async")) return rc;
+    if (int rc = use_device(m->ctx)) return rc;
     ML2_CUDA(cudaMemcpyAsync(m->tokens + pos, token_pinned_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
     return ML2_OK;
 }
@@ -1038,14 +1102,15 @@ int ml2_model_step_host(ml2_model* h, int pos, const int* token_in_pinned_host, 
     if (!m || !token_in_pinned_host || !token_out_host) return fail(ML2_E_INVALID, "step_host: null argument");
     if (pos < 0 || pos + 1 > m->cfg.seq_len) return fail(ML2_E_INVALID, "step_host: pos=%d", pos);
     if (!m->tokens) return fail(ML2_E_STATE, "step_host: run state missing");
+    if (int rc0 = check_token_ids(m, token_in_pinned_host, 1, "step_host")) return rc0;
+    if (int rc0 = use_device(m->ctx)) return rc0;
     // host -> device: this step's input token; the step; device -> host: the sampled token (the reference's blocking
     // 4-byte read, src/Sampler.cs:69)
     ML2_CUDA(cudaMemcpyAsync(m->tokens + pos, token_in_pinned_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
     const int rc = ml2_model_forward(h, pos, pos + 1, 1);
     if (rc) return rc;
     ML2_CUDA(cudaMemcpyAsync(token_out_host, m->tokens + pos + 1, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
-    ML2_CUDA(cudaStreamSynchronize(m->stream));
-    return ML2_OK;
+    return check_device_status(m);   // synchronises: the token and the error word arrive together
 }
 
 int ml2_model_read_token(ml2_model* h, int pos, int* token_host)
@@ -1054,9 +1119,9 @@ int ml2_model_read_token(ml2_model* h, int pos, int* token_host)
     if (!m || !token_host) return fail(ML2_E_INVALID, "read_token: null argument");
     if (pos < 0 || pos > m->cfg.seq_len) return fail(ML2_E_INVALID, "read_token: pos");
     // the reference's only per-token synchronisation: a 4-byte blocking read (src/Sampler.cs:69)
+    if (int rc = use_device(m->ctx)) return rc;
     ML2_CUDA(cudaMemcpyAsync(token_host, m->tokens + pos, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
-    ML2_CUDA(cudaStreamSynchronize(m->stream));
-    return ML2_OK;
+    return check_device_status(m);
 }
 
 int ml2_model_sample(ml2_model* h, int next_pos, float temperature, float top_p, float coin)
@@ -1083,9 +1148,9 @@ int ml2_model_read_logits(ml2_model* h, void* logits_host_f16)
     Model* m = reinterpret_cast<Model*>(h);
     if (!m || !logits_host_f16) return fail(ML2_E_INVALID, "read_logits: null argument");
     const __half* src = (m->mega_ok && m->logits_view) ? m->logits_view : m->logits;
+    if (int rc = use_device(m->ctx)) return rc;
     ML2_CUDA(cudaMemcpyAsync(logits_host_f16, src, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, m->stream));
-    ML2_CUDA(cudaStreamSynchronize(m->stream));
-    return ML2_OK;
+    return check_device_status(m);
 }
 
 int ml2_model_debug_prof(ml2_model* h, long long* out, int n)
@@ -1094,6 +1159,27 @@ int ml2_model_debug_prof(ml2_model* h, long long* out, int n)
     if (!m || !out || !m->mega_prof) return fail(ML2_E_STATE, "no profile buffer (set ML2_MEGA_PROF=1 before the first forward)");
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     ML2_CUDA(cudaMemcpy(out, m->mega_prof, (size_t)std::min(n, m->mega_grid * 64) * sizeof(long long), cudaMemcpyDeviceToHost));
+    return ML2_OK;
+}
+
+int ml2_model_set_split_attention_from(ml2_model* h, int min_seq)
+{
+    // From this many cache rows on, the persistent kernel spreads every head's attention over several CTAs.
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    if (min_seq < 2) return fail(ML2_E_INVALID, "set_split_attention_from: %d (at least 2)", min_seq);
+    m->att_min_seq = min_seq;
+    return ML2_OK;
+}
+
+int ml2_model_debug_skip_launch(ml2_model* h)
+{
+    // Host-made desynchronisation for the failure-path test: advances the launch number the counters are compared
+    // with, exactly what a rank that skipped a forward looks like to its peers. The next forward's dependency waits
+    // can then never be met and run out after the context's wait limit; nothing on the device is touched here.
+    Model* m = reinterpret_cast<Model*>(h);
+    if (!m) return fail(ML2_E_INVALID, "null model");
+    ++m->mega_seq;
     return ML2_OK;
 }
 
@@ -1155,13 +1241,18 @@ int ml2_model_profile(ml2_model* h, int iters, double* avg_us, double* algo_byte
     if (rc) return rc;
     if (iters < 1) return fail(ML2_E_INVALID, "profile: iters=%d", iters);
     Ctx* ctx = m->ctx;
+    if ((rc = use_device(ctx))) return rc;
     ctx->stream = m->stream;
     const ml2_config& c = m->cfg;
     __half* x_save = nullptr;
     ML2_CUDA(cudaMalloc(&x_save, (size_t)c.dim * 2));
     ML2_CUDA(cudaMemcpyAsync(x_save, m->x, (size_t)c.dim * 2, cudaMemcpyDeviceToDevice, m->stream));
-    int pos = 0;
-    ML2_CUDA(cudaMemcpyAsync(&pos, &m->step->pos, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    // the attention is timed at the position of the latest forward (its cache rows are written up to there)
+    const int pos = m->last_pos;
+    {
+        StepState st{pos, pos + 1, 0, 0};
+        ML2_CUDA(cudaMemcpyAsync(m->step, &st, sizeof(st), cudaMemcpyHostToDevice, m->stream));
+    }
     ML2_CUDA(cudaStreamSynchronize(m->stream));
     cudaEvent_t e0, e1;
     ML2_CUDA(cudaEventCreate(&e0));
@@ -1223,9 +1314,8 @@ int ml2_model_generate(ml2_model* h, const int* prompt_host, int n_prompt, int s
         if (token < 3) break;
         out_tokens_host[produced++] = token;
     }
-    ML2_CUDA(cudaStreamSynchronize(m->stream));
     *n_out = produced;
-    return ML2_OK;
+    return check_device_status(m);
 }
 
 }  // extern "C"

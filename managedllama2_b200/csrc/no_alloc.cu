@@ -26,16 +26,14 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticInBytes +
 static std::mutex g_static_mutex;
 static unsigned char* g_static_ptr[64] = {};
 
-// One-time set-up for `device` (made current here): resolves the array's device address.
+// One-time set-up for `device` (the caller has made it current): resolves the array's device address.
 static int static_scratch_for(int device, unsigned char** out)
 {
     if (device < 0 || device >= 64) return fail(ML2_E_INVALID, "static scratch: device %d out of range", device);
     std::lock_guard<std::mutex> lock(g_static_mutex);
     if (!g_static_ptr[device]) {
-        cudaError_t e = cudaSetDevice(device);
-        if (e != cudaSuccess) return fail(ML2_E_CUDA, "static scratch: cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
         unsigned char* p = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
         if (e != cudaSuccess || !p) return fail(ML2_E_CUDA, "static scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
         g_static_ptr[device] = p;
     }
@@ -59,8 +57,9 @@ extern "C" int ml2_matvec_residual_int4_host_static(ml2_ctx* h, void* inout_host
                     "outputs); use ml2_matvec_residual_int4_host or device buffers for larger vectors",
                     rows, cols, kStaticMaxRows, kStaticMaxCols);
     unsigned char* base = nullptr;
-    int rc = static_scratch_for(ctx->device, &base);
+    int rc = use_device(ctx);   // on every call, not only the first: the symbol look-up and the copies below go to this device
     if (rc) return rc;
+    if ((rc = static_scratch_for(ctx->device, &base))) return rc;
     // Both regions are fully overwritten by the copies below before the kernel reads them, so nothing has
     // to be cleared between calls; what an earlier call left behind is never observed.
     unsigned char* d_in = base;

@@ -62,7 +62,6 @@ struct MatVecParams {
     int woff_z, woff_s;        // byte offsets of the zeros / scales sub-regions inside a chunk
     int ntiles;                // stage-tiles in the whole problem
     int head_size;
-    int debug;                 // bit 0: consumers skip the arithmetic (pipeline probe)
 };
 
 struct Chunk {
@@ -289,8 +288,10 @@ __device__ __forceinline__ void wait_parked_or_abort(uint64_t* bar, uint32_t par
     }
 }
 
-template <Fmt F, Epi E, Pro P, int RW>
-__global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecParams p)
+// kMaxThreads: the largest block this instantiation is launched with (512 or 1024; the plan's block is
+// (k-warps x chunks + 2) warps), so that the register allocation matches the real block size.
+template <Fmt F, Epi E, Pro P, int RW, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads, 1) stream_matvec_kernel(const MatVecParams p)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];    // producer -> consumers: stage landed
@@ -347,7 +348,7 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
             const uint32_t* gz = nullptr;
             const __half* gs = nullptr;
             uint32_t bz = 0, bs = 0;
-            if (F == Fmt::Int4 && !(p.debug & 2)) {
+            if (F == Fmt::Int4) {
                 gz = q.z + (size_t)c.row0 * p.zsize;
                 gs = q.s + (size_t)c.row0 * p.ssize;
                 bz = (uint32_t)c.nrows * p.zsize * 4u;
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
             if (live && fast) {
                 unsigned char* cb = sbase + (size_t)lane * p.chunk_bytes;
                 bulk_g2s(cb, gw, bw, &full_bar[st], pol);
-                if (F == Fmt::Int4 && !(p.debug & 2)) {
+                if (F == Fmt::Int4) {
                     bulk_g2s(cb + p.woff_z, gz, bz, &full_bar[st], pol);
                     bulk_g2s(cb + p.woff_s, gs, bs, &full_bar[st], pol);
                 }
@@ -508,10 +509,7 @@ __global__ void __launch_bounds__(1024, 1) stream_matvec_kernel(const MatVecPara
         wait_or_abort(&full_bar[st], (i / p.nstage) & 1, &s_abort, p.status, 2u, i);
         const uint32_t cb = chunk_base + (uint32_t)st * stage_bytes;
         float v[RW];
-        if (p.debug & 1) {
-#pragma unroll
-            for (int r = 0; r < RW; ++r) v[r] = 0.f;
-        } else if constexpr (F == Fmt::Int4) {
+        if constexpr (F == Fmt::Int4) {
             uint4 wv[RW];
 #pragma unroll
             for (int r = 0; r < RW; ++r)

@@ -57,6 +57,10 @@ class CudaContext:
     def synchronize(self):
         _lib.check(self._lib.ml2_ctx_synchronize(self.handle))
 
+    def set_wait_limit(self, sm_cycles):
+        """Budget of every device-side wait, in SM clock cycles (default about two seconds)."""
+        _lib.check(self._lib.ml2_ctx_set_wait_limit(self.handle, ctypes.c_longlong(int(sm_cycles))))
+
     def status(self):
         err, det = ctypes.c_uint(), ctypes.c_uint()
         _lib.check(self._lib.ml2_ctx_status(self.handle, ctypes.byref(err), ctypes.byref(det)))

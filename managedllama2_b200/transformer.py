@@ -246,6 +246,19 @@ class _FileLayerStruct(ctypes.Structure):
     _fields_ = _LayerStruct._fields_
 
 
+def tp_forward_counts_agree(dist, count):
+    """True when every rank of `dist` reports the same number of Forward calls; raises RuntimeError otherwise."""
+    import torch
+    mine = torch.tensor([int(count)], dtype=torch.int64)
+    world = dist.get_world_size()
+    all_counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(all_counts, mine)
+    counts = [int(t.item()) for t in all_counts]
+    if len(set(counts)) != 1:
+        raise RuntimeError("tensor-parallel ranks are out of step: Forward counts per rank %s" % counts)
+    return True
+
+
 class Transformer:
     """src/Transformer.cs on token ids. ``Forward`` is one CUDA-graph replay of the fused per-token sequence."""
 
@@ -373,6 +386,21 @@ class Transformer:
 
     def synchronize(self):
         _lib.check(self.lib.ml2_model_synchronize(self.handle))
+
+    def forward_count_in_step(self, dist, count):
+        """Host rule of the tensor-parallel persistent kernel: every rank calls Forward the same number of times (a
+        rank that skipped one leaves its peers waiting for arrivals that never come). Gathers the ranks' counts over
+        `dist` (any backend) and raises on the first mismatch, before anything is launched."""
+        return tp_forward_counts_agree(dist, count)
+
+    def set_split_attention_from(self, min_seq):
+        """Sequence length from which the persistent kernel splits a head's attention over several CTAs (default 704)."""
+        _lib.check(self.lib.ml2_model_set_split_attention_from(self.handle, ctypes.c_int(int(min_seq))))
+
+    def reset(self):
+        """After an Ml2Error with code ML2_E_DEVICE (a kernel's bounded wait ran out): clears the error and the
+        counters the persistent kernel keeps between tokens. Under tensor parallelism every rank calls it."""
+        _lib.check(self.lib.ml2_model_reset(self.handle))
 
     @property
     def launches_per_token(self):

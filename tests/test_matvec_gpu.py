@@ -88,15 +88,30 @@ def test_qkv_matvec_int4(ctx, rows, cols):
 
 @pytest.mark.parametrize("rows,cols", [(128, 128), (4096, 11008), (5120, 13824), (512, 90)])
 def test_matvec_swiglu_int4(ctx, rows, cols):
+    """The gate and up mat-vecs are each held to the 1e-3 of every mat-vec output (through ml2_matvec_int4 on the same
+    weights and input); the fused output silu(g) * u then carries both errors: with |dg|, |du| <= 1e-3 (relative to the
+    larger of the value and the vector's rms) and |d silu / dg| <= 1.1, the product is within (1.1 + 1) * 1e-3 = 2.1e-3
+    plus its own fp16 rounding (4.9e-4): the bound asserted below is 2.6e-3."""
+    import ctypes
     import torch
     import managedllama2_b200 as ml2
+    from managedllama2_b200 import _lib
     rng = np.random.default_rng(rows + 5 * cols)
     g, u = rand_qweight(rng, rows, cols), rand_qweight(rng, rows, cols)
     x = rand_vec(rng, rows, 0.3)
+    xd = to_dev(x)
+    for q in (g, u):
+        dq = dev_qweight(*q)
+        qs = dq.struct()
+        part = torch.zeros(cols, dtype=torch.float16, device="cuda")
+        _lib.check(ctx._lib.ml2_matvec_int4(ctx.handle, ctypes.c_void_p(part.data_ptr()), ctypes.c_void_p(xd.data_ptr()),
+                                            ctypes.byref(qs), rows, cols))
+        zero = np.zeros(cols, np.float16)
+        assert rel_err(to_host(part), oracle.matvec_residual_int4(zero, x, *q, rows, cols, mode=1)) <= TOL
     want = oracle.matvec_swiglu_int4(x, g, u, rows, cols, mode=1)
     out = torch.zeros(cols, dtype=torch.float16, device="cuda")
-    ml2.MatVecSwiGLU(ctx).Forward(out, to_dev(x), dev_qweight(*g), dev_qweight(*u), rows, cols)
-    assert rel_err(to_host(out), want) <= 2 * TOL  # product of two rounded-once sums
+    ml2.MatVecSwiGLU(ctx).Forward(out, xd, dev_qweight(*g), dev_qweight(*u), rows, cols)
+    assert rel_err(to_host(out), want) <= 2.6 * TOL
 
 
 @pytest.mark.parametrize("rows,cols", [(4096, 64), (4096, 32000), (5120, 1000), (264, 7)])

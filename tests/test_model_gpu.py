@@ -134,14 +134,14 @@ def test_long_sequence_cluster_path():
 
 
 @pytest.mark.parametrize("heads", [2, 5])
-def test_split_attention_in_the_persistent_kernel(monkeypatch, heads):
+def test_split_attention_in_the_persistent_kernel(heads):
     """Several CTAs per head (the long-context path of the persistent kernel), forced on from the second position so
     that parts without any cache row, one-row parts and uneven parts all occur; logits against the oracle."""
     import managedllama2_b200 as ml2
-    monkeypatch.setenv("ML2_ATT_MIN_SEQ", "2")
     cfg = ml2.Config(dim=128 * heads, hiddenDim=384, numLayers=2, numHeads=heads, numKVHeads=heads, vocabSize=256, seqLength=300)
     ctx = ml2.CudaContext(0)
     tr = ml2.Transformer(cfg, ml2.synthetic_weights(ctx, cfg, seed=6), ctx)
+    tr.set_split_attention_from(2)
     cpu, _ = oracle_model(ml2, cfg, 6)
     rng = np.random.default_rng(3)
     toks = rng.integers(3, cfg.vocabSize, size=cfg.seqLength).astype(np.int32)
@@ -163,13 +163,15 @@ def test_peaked_attention_matches_oracle(mode):
     softmax is far from uniform and a wrong score, rotation or cache row shows in the logits at once; with the small
     weights of the benchmark construction every position gets nearly the same probability and such an error hides."""
     import managedllama2_b200 as ml2
-    env = {"persistent": {}, "persistent_split": {"ML2_ATT_MIN_SEQ": "2"}, "graph": {"ML2_NO_MEGA": "1"},
+    env = {"persistent": {}, "persistent_split": {}, "graph": {"ML2_NO_MEGA": "1"},
            "eager": {"ML2_NO_MEGA": "1", "ML2_NO_GRAPH": "1"}}[mode]
     os.environ.update(env)
     try:
         cfg = ml2.Config(dim=384, hiddenDim=640, numLayers=2, numHeads=3, numKVHeads=3, vocabSize=320, seqLength=200)
         ctx = ml2.CudaContext(0)
         tr = ml2.Transformer(cfg, ml2.synthetic_weights(ctx, cfg, seed=13, sigma=1.0), ctx)
+        if mode == "persistent_split":
+            tr.set_split_attention_from(2)
     finally:
         for k in env:
             os.environ.pop(k, None)
@@ -215,4 +217,33 @@ def test_step_host_equals_forward_and_read():
         assert tok_a == tok_b, pos
     a.close()
     b.close()
+    ctx.close()
+
+
+def test_long_context_to_4096_through_the_split_attention():
+    """The longest context of the benchmark configurations (4096 positions) on a small model: one CTA per head up to 703
+    cache rows, several CTAs per head from 704 on (the default threshold). Logits against the oracle around the switch
+    and over the last 64 positions; unit-scale weights, so the attention is peaked and every cache row matters."""
+    import managedllama2_b200 as ml2
+    cfg = ml2.Config(dim=256, hiddenDim=384, numLayers=1, numHeads=2, numKVHeads=2, vocabSize=256, seqLength=4096)
+    ctx = ml2.CudaContext(0)
+    tr = ml2.Transformer(cfg, ml2.synthetic_weights(ctx, cfg, seed=17, sigma=1.0), ctx)
+    hw = ml2.synthetic_weights_host(cfg, seed=17, sigma=1.0)
+    cpu = oracle.CpuModel(dict(dim=cfg.dim, hidden_dim=cfg.hiddenDim, n_layers=cfg.numLayers, n_heads=cfg.numHeads,
+                               n_kv_heads=cfg.numKVHeads, vocab_size=cfg.vocabSize, seq_len=cfg.seqLength,
+                               rope_theta=cfg.ropeTheta), hw, mode=1)
+    rng = np.random.default_rng(9)
+    toks = rng.integers(3, cfg.vocabSize, size=cfg.seqLength).astype(np.int32)
+    tr.set_tokens(toks)
+    checked = 0
+    for pos in range(cfg.seqLength - 1):
+        tr.Forward(pos, pos + 1, False)
+        want = cpu.forward(toks[pos], pos).astype(np.float32)
+        if pos in (0, 1, 702, 703, 704, 705, 1500, 2047, 2048) or pos >= 4031:
+            got = tr.logits().astype(np.float32)
+            assert np.abs(got - want).max() <= 2e-2 * want.std(), pos
+            checked += 1
+    assert checked >= 70 and tr.launches_per_token == 1
+    assert ctx.status() == (0, 0)
+    tr.close()
     ctx.close()

@@ -69,13 +69,14 @@ def test_swiglu_and_qkv_vs_reference_kernels(kernels):
     ctx.close()
 
 
-def test_small_ops_vs_reference_kernels(kernels):
+@pytest.mark.parametrize("seq", [300, 4096])
+def test_small_ops_vs_reference_kernels(kernels, seq):
     """RMSNorm, RoPE (bit-exact: same device math functions), scores, softmax, values, argmax."""
     import torch
     import managedllama2_b200 as ml2
     rng = np.random.default_rng(5)
-    dim, heads, seq = 4096, 32, 300
-    cfg = ml2.Config(dim, 11008, 1, heads, heads, 32000, 512)
+    dim, heads = 4096, 32   # seq 4096: the longest context of the benchmark configurations (the reference's softmax holds 8192)
+    cfg = ml2.Config(dim, 11008, 1, heads, heads, 32000, max(512, seq))
     ref = ref_cuda.RefModules(cfg, kernels)
     ctx = ml2.CudaContext(0)
     x, gamma = to_dev(rand_vec(rng, dim)), to_dev(rand_vec(rng, dim, 0.02))
@@ -119,12 +120,20 @@ def test_small_ops_vs_reference_kernels(kernels):
     ctx.close()
 
 
-def test_greedy_decode_7b_shape_vs_reference_cuda_build(kernels):
+SHAPES = {
+    # the two model shapes the benchmark configurations name; their operator plans differ (7B: 4 warps per row, 5 groups;
+    # 13B: 5 warps per row, 4 groups, and 7 warps with two weight vectors per lane for the 13824-wide down-projection)
+    "7b": dict(dim=4096, hiddenDim=11008, numLayers=32, numHeads=32, numKVHeads=32, vocabSize=32000),
+    "13b": dict(dim=5120, hiddenDim=13824, numLayers=40, numHeads=40, numKVHeads=40, vocabSize=32000),
+}
+
+
+@pytest.mark.parametrize("shape", ["7b", "13b"])
+def test_greedy_decode_vs_reference_cuda_build(kernels, shape):
     import torch
     import managedllama2_b200 as ml2
     prompt_len, gen = 16, 64
-    cfg = ml2.Config(dim=4096, hiddenDim=11008, numLayers=32, numHeads=32, numKVHeads=32, vocabSize=32000,
-                     seqLength=prompt_len + gen + 4)
+    cfg = ml2.Config(seqLength=prompt_len + gen + 4, **SHAPES[shape])
     ctx = ml2.CudaContext(0)
     w = ml2.synthetic_weights(ctx, cfg, seed=31415)
     ours = ml2.Transformer(cfg, w, ctx)
@@ -155,7 +164,8 @@ def test_greedy_decode_7b_shape_vs_reference_cuda_build(kernels):
                 ours.set_tokens(np.array([t_ref], dtype=np.int32), first=pos + 1)  # continue on the reference's tokens
     assert checked == gen
     assert flips <= 2
-    print("7B-shape greedy decode vs reference CUDA kernels: max |dlogit| = %.3e over %d steps, %d near-tie flips" %
-          (worst, prompt_len + gen - 1, flips))
+    assert ours.launches_per_token == 1, "the persistent kernel is the path under test"
+    print("%s-shape greedy decode vs reference CUDA kernels: max |dlogit| = %.3e over %d steps, %d near-tie flips" %
+          (shape, worst, prompt_len + gen - 1, flips))
     ours.close()
     ctx.close()

@@ -101,7 +101,7 @@ def test_softmax_reference_cases(ctx):
         assert abs(float(got.astype(np.float32).sum()) - 1.0) < 5e-3
 
 
-@pytest.mark.parametrize("heads,size", [(32, 1), (32, 33), (40, 1000), (2, 9000)])
+@pytest.mark.parametrize("heads,size", [(32, 1), (32, 33), (40, 1000), (40, 4096), (2, 9000)])
 def test_softmax_sizes(ctx, heads, size):
     """Up to and beyond the reference's 8192-float shared-memory cap (native/softmax_kernel.cu:5)."""
     import managedllama2_b200 as ml2
@@ -149,7 +149,7 @@ def test_embedding_reference_case(ctx):
         assert np.array_equal(to_host(out).view(np.uint16), table[t * size:(t + 1) * size].view(np.uint16))
 
 
-@pytest.mark.parametrize("seq", [1, 16, 31, 32, 33, 272])
+@pytest.mark.parametrize("seq", [1, 16, 31, 32, 33, 272, 4096])
 def test_scores_and_values_reference_shapes(ctx, seq):
     """test/MatVecStridedTests.cs:74-92 and test/VecMatTests.cs:75-93: dim 4096, 32 heads, seq 16 (and other lengths)."""
     import torch

@@ -78,3 +78,39 @@ def test_two_rank_sharded_ffn_matches_unsharded():
     assert same
     assert hng == 3
     assert err <= 1e-3
+
+
+def _lockstep_worker(rank, world, port, q):
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from managedllama2_b200.transformer import tp_forward_counts_agree
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok_equal = tp_forward_counts_agree(dist, 7)
+    # rank 1 "skipped" a forward: every rank must find out on the host, before any launch
+    try:
+        tp_forward_counts_agree(dist, 8 if rank == 0 else 7)
+        caught = False
+    except RuntimeError as e:
+        caught = "out of step" in str(e)
+    q.put((rank, ok_equal, caught))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_out_of_step_are_found_on_the_host():
+    """Host rule of the fused tensor-parallel path: all ranks call Forward the same number of times. A rank that skips
+    one would leave its peers' kernels waiting for arrivals that never come (they give up after the wait limit); the
+    check finds the mismatch on the host, with no GPU involved."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_lockstep_worker, args=(r, 2, 29512, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, True, True), (1, True, True)]

@@ -21,6 +21,21 @@ def test_tensor_parallel_matches_oracle(world):
     assert out.returncode == 0 and "TP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_13b_shape_matches_oracle(world):
+    """The shape the benchmark times (40 heads, 108 hidden groups of 128), cut to 2 layers: logits identical on every
+    rank bit for bit and within tolerance of the unsharded CPU oracle."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "0"), ML2_TP_SHAPE="13b")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
+           "127.0.0.1", "--master-port", str(29620 + world), os.path.join(here, "tp_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0 and "TP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
 def test_tensor_parallel_from_model_bin(tmp_path):
     """Two ranks load their shards from one model.bin (the reference's file layout) and match the oracle."""
     import torch

@@ -24,8 +24,12 @@ def main():
     if rank == 0:
         idt = torch.frombuffer(bytearray(ml2.Transformer.nccl_unique_id()), dtype=torch.uint8).cuda()
     dist.broadcast(idt, 0)
-    # 8 heads, 13 hidden groups: uneven hidden split for 2, 4 and 8 ranks
-    cfg = ml2.Config(dim=1024, hiddenDim=13 * 128, numLayers=2, numHeads=8, numKVHeads=8, vocabSize=512, seqLength=40)
+    if os.environ.get("ML2_TP_SHAPE") == "13b":
+        # the benchmark's shape cut to 2 layers: 40 heads and 108 hidden groups, so 8 ranks see 5 heads and 14 / 13 groups
+        cfg = ml2.Config(dim=5120, hiddenDim=13824, numLayers=2, numHeads=40, numKVHeads=40, vocabSize=32000, seqLength=40)
+    else:
+        # 8 heads, 13 hidden groups: uneven hidden split for 2, 4 and 8 ranks
+        cfg = ml2.Config(dim=1024, hiddenDim=13 * 128, numLayers=2, numHeads=8, numKVHeads=8, vocabSize=512, seqLength=40)
     ctx = ml2.CudaContext(local)
     model_bin = os.environ.get("ML2_TP_MODEL_BIN")
     if model_bin:
@@ -42,6 +46,7 @@ def main():
     if os.environ.get("ML2_TP_FUSED", "1") == "1":
         tr.attach_peers_with(dist)   # one persistent kernel per token, all-reduce over peer memory
     toks = [5, 99, 256, 31]
+    steps = 8 if os.environ.get("ML2_TP_SHAPE") == "13b" else 12
     tr.set_tokens(np.array(toks, dtype=np.int32))
     cpu = None
     if rank == 0:
@@ -50,7 +55,7 @@ def main():
                                    n_kv_heads=cfg.numKVHeads, vocab_size=cfg.vocabSize, seq_len=cfg.seqLength,
                                    rope_theta=cfg.ropeTheta), hw, mode=1)
     ok = True
-    for pos in range(12):
+    for pos in range(steps):
         gen = pos + 1 >= len(toks)
         tr.Forward(pos, pos + 1, gen)
         logits = tr.logits()
