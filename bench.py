@@ -7,21 +7,26 @@ A step is one decoded token (one pass of the per-token operator sequence + the g
 --gpus N > 1 the script is started once per GPU by torch.distributed.run and the model runs tensor
 parallel over the N ranks (total work fixed: strong scaling). Rank 0 prints ONE JSON line.
 
-  value     tokens/s with everything resident on the device (CUDA events on the model's stream)
-  e2e       tokens/s through the host-buffer API: per step the token id goes host->device (4 B, pinned),
-            the forward runs, and the sampled id comes back device->host (4 B), as a host-driven loop does
-  roofline  the dominant kernel (gate/up int4 mat-vec + SwiGLU) timed alone over all layers
-  kernels   the same for every kernel kind
-  cpu_baseline  the CPU oracle (C restatement of the reference's C# CPU code) on this box's cores, on a
-            bounded sample (a few layers) extrapolated to one token
+  value          tokens/s with everything resident on the device (CUDA events on the model's stream)
+  e2e            tokens/s through the host-buffer API: per step the token id goes host->device (4 B, pinned),
+                 the forward runs, and the sampled id comes back device->host (4 B), as a host-driven loop does
+  roofline       the persistent per-token kernel: algorithmic bytes of one launch / its duration
+  long_context   the same decode after a 4032-token prompt prefilled token by token (64 steps up to position 4096)
+  matvec_single  one 4096 -> 4096 int4 mat-vec over 32 rotating weight sets (independent launches and a chain with
+                 programmatic dependent launch), and the mat-vec set of one 7B-shape layer
+  kernels_timed_alone   every per-operator kernel of the graph path swept over all layers, chained as that path runs them
+  tp_check       (N > 1) a 2-layer cut of the same shape, sharded like the timed model, against the CPU oracle
+  cpu_baseline   the CPU oracle (C restatement of the reference's C# CPU code) on this box's cores: whole tokens
 
---impl reference times that CPU restatement as the reference arm (the reference's C# cannot be built
-here and its CUDA kernels are not a CPU implementation).
+--impl reference times that CPU restatement on whole tokens of the same configuration (the reference's C# cannot be
+built here and its CUDA kernels are not a CPU implementation); it needs neither a GPU nor the product library.
 """
 import argparse
 import ctypes
+import hashlib
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -33,11 +38,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CONFIGS = {
-    # BASELINE configs[3] / configs[2]
     "13b": dict(dim=5120, hiddenDim=13824, numLayers=40, numHeads=40, numKVHeads=40, vocabSize=32000),
     "7b": dict(dim=4096, hiddenDim=11008, numLayers=32, numHeads=32, numKVHeads=32, vocabSize=32000),
 }
 PROMPT_LEN = 16
+LONG_PROMPT = 4032
+LONG_STEPS = 64
 SEED = 31415
 
 
@@ -49,6 +55,16 @@ def measured_peak_gbs():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def profiled_traffic_ratio():
+    """DRAM bytes moved per algorithmic byte of the persistent kernel, from the kept ncu summary (None when absent)."""
+    p = os.path.join(ROOT, "profiles", "decode_token_kernel_13b_8layers.md")
+    try:
+        m = re.search(r"dram_bytes_per_algorithmic_byte\s*=\s*([0-9.]+)", open(p).read())
+        return float(m.group(1)) if m else None
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -100,93 +116,114 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def qweight_bytes(rows, cols):
+    ss = -(-rows // 128)
+    return cols * ((-(-rows // 32)) * 16 + (-(-ss // 8)) * 4 + ss * 2)
+
+
 def token_bytes(cfg, tp=1):
     """Algorithmic bytes one token reads on one rank (weights + classifier + norms + embedding row), KV excluded."""
-    def qw(rows, cols):
-        ss = -(-rows // 128)
-        return cols * ((-(-rows // 32)) * 16 + (-(-ss // 8)) * 4 + ss * 2)
     d, h, L, V = cfg["dim"], cfg["hiddenDim"], cfg["numLayers"], cfg["vocabSize"]
-    per_layer = 3 * qw(d, d // tp) + qw(d // tp, d) + 2 * qw(d, h // tp) + qw(h // tp, d) + 2 * d * 2
+    per_layer = 3 * qweight_bytes(d, d // tp) + qweight_bytes(d // tp, d) + 2 * qweight_bytes(d, h // tp) + qweight_bytes(h // tp, d) + 2 * d * 2
     return L * per_layer + (V // tp) * d * 2 + d * 2 + d * 2
 
 
+def config_block(args, cfg, world):
+    """The `config` object of the JSON line: the same for both arms of one command line."""
+    tb = token_bytes(cfg, world)
+    return {"workload": "llama2-%s-shape%s AWQ int4 g128, batch-1 greedy decode, %d-token prompt then decode" %
+                        (args.config, (" cut to %d layers" % args.layers) if args.layers else "", PROMPT_LEN) +
+                        ((" from position %d" % args.context) if args.context else ""),
+            "parallelism": "tp%d" % world, "l2": "per-token working set %.2f GB per GPU, far larger than L2" % (tb / 1e9),
+            "bytes_per_token_per_gpu": tb}
+
+
+def oracle_cfg(cfg, seq_len):
+    return dict(dim=cfg["dim"], hidden_dim=cfg["hiddenDim"], n_layers=cfg["numLayers"], n_heads=cfg["numHeads"],
+                n_kv_heads=cfg["numKVHeads"], vocab_size=cfg["vocabSize"], seq_len=seq_len, rope_theta=10000.0)
+
+
 # --------------------------------------------------------------------------------------------------
-# CPU arm: the oracle (C restatement of the reference's C# CPU reference) on the host cores
+# CPU arm: the oracle (C restatement of the reference's C# CPU reference) on the host cores, WHOLE tokens
 # --------------------------------------------------------------------------------------------------
-def cpu_layer_sampler(cfg, threads):
-    """Returns (run_layer, run_classifier): closures timing one layer's mat-vec set / the classifier on the CPU."""
+def cpu_whole_tokens(cfg, threads, max_tokens, budget_s, warm_tokens=0):
+    """Decodes whole tokens of `cfg` with the oracle in the reference's CPU arithmetic (every weight unpacked to fp16,
+    sequential fp32 dot: test/MatVecInt4Tests.cs:48-70 with src/QWeight.cs:29-54), `threads` threads over output rows.
+    Returns (seconds per token list, seconds spent building the model)."""
     import oracle
-    import managedllama2_b200 as ml2
+    oracle.build()
     oracle.set_threads(threads)
-    c = ml2.Config(seqLength=64, **cfg)
-    one = ml2.Config(dim=c.dim, hiddenDim=c.hiddenDim, numLayers=1, numHeads=c.numHeads, numKVHeads=c.numKVHeads,
-                     vocabSize=256, seqLength=64)
-    hw = ml2.synthetic_weights_host(one, seed=SEED)
-    L = hw["layers"][0]
-    rng = np.random.default_rng(1)
-    x = rng.standard_normal(c.dim).astype(np.float16)
-    hvec = (rng.standard_normal(c.hiddenDim) * 0.1).astype(np.float16)
-    cls = (rng.standard_normal((2000, c.dim)) * 0.02).astype(np.float16)  # a 2000-row slice of the classifier
-
-    def run_layer():
-        # the seven int4 mat-vecs of one layer in the C# reference arithmetic (unpack to fp16, fp32 dot) + norms
-        xb = oracle.rmsnorm(x, L["rms_att"])
-        oracle.qkv_matvec_int4(xb, L["q"], L["k"], L["v"], c.dim, c.dim, mode=0)
-        oracle.matvec_residual_int4(x, xb, *L["o"], c.dim, c.dim, mode=0)
-        xb = oracle.rmsnorm(x, L["rms_ffn"])
-        oracle.matvec_swiglu_int4(xb, L["gate"], L["up"], c.dim, c.hiddenDim, mode=0)
-        oracle.matvec_residual_int4(x, hvec, *L["down"], c.hiddenDim, c.dim, mode=0)
-
-    def run_classifier_slice():
-        oracle.matvec_f16(x, cls, c.dim, cls.shape[0])
-
-    return run_layer, run_classifier_slice, cls.shape[0]
-
-
-def cpu_tokens_per_s(cfg, threads, layer_reps):
-    run_layer, run_cls, cls_rows = cpu_layer_sampler(cfg, threads)
-    run_layer()
     t0 = time.perf_counter()
-    for _ in range(layer_reps):
-        run_layer()
-    t_layer = (time.perf_counter() - t0) / layer_reps
+    oc = oracle_cfg(cfg, 64)
+    model = oracle.CpuModel(oc, oracle.synthetic_weights(oc, seed=SEED), mode=0)
+    t_build = time.perf_counter() - t0
+    rng = np.random.default_rng(SEED)
+    toks = rng.integers(3, cfg["vocabSize"], size=64)
+    pos = 0
+    for _ in range(warm_tokens):
+        model.forward(int(toks[pos]), pos)
+        pos += 1
+    times = []
+    start = time.perf_counter()
+    while len(times) < max_tokens:
+        t0 = time.perf_counter()
+        model.forward(int(toks[pos]), pos)
+        times.append(time.perf_counter() - t0)
+        pos += 1
+        if time.perf_counter() - start > budget_s:
+            break
+    return times, t_build
+
+
+def cpu_single_thread_small_cases():
+    """The reference's CPU arithmetic on ONE thread, as the reference runs it: one 4096 -> 4096 int4 mat-vec and the
+    seven mat-vecs of a 7B-shape layer (QKV, o-proj with residual, gate/up with SwiGLU, down with residual)."""
+    import oracle
+    oracle.set_threads(1)
+    rng = np.random.default_rng(7)
+
+    def qw(rows, cols):
+        nw, nz, ns = oracle.qweight_sizes(rows)
+        return (rng.integers(0, 1 << 32, size=cols * nw, dtype=np.uint32), rng.integers(0, 1 << 32, size=cols * nz, dtype=np.uint32),
+                (0.001 + 0.019 * rng.random(cols * ns, dtype=np.float32)).astype(np.float16))
+    d, h = 4096, 11008
+    x = rng.standard_normal(d).astype(np.float16)
+    res = rng.standard_normal(d).astype(np.float16)
+    hv = (rng.standard_normal(h) * 0.1).astype(np.float16)
+    a = qw(d, d)
+    oracle.matvec_residual_int4(res, x, *a, d, d, mode=0)
     t0 = time.perf_counter()
-    run_cls()
-    t_cls = (time.perf_counter() - t0) * cfg["vocabSize"] / cls_rows
-    return 1.0 / (cfg["numLayers"] * t_layer + t_cls), t_layer, t_cls
+    oracle.matvec_residual_int4(res, x, *a, d, d, mode=0)
+    t_one = time.perf_counter() - t0
+    q, k, v, o, g, u, dn = qw(d, d), qw(d, d), qw(d, d), a, qw(d, h), qw(d, h), qw(h, d)
+    t0 = time.perf_counter()
+    oracle.qkv_matvec_int4(x, q, k, v, d, d, mode=0)
+    oracle.matvec_residual_int4(res, x, *o, d, d, mode=0)
+    oracle.matvec_swiglu_int4(x, g, u, d, h, mode=0)
+    oracle.matvec_residual_int4(res, hv, *dn, h, d, mode=0)
+    t_layer = time.perf_counter() - t0
+    return {"threads": 1, "matvec_4096x4096_ms": t_one * 1e3, "matvec_4096x4096_GB/s": qweight_bytes(d, d) / t_one / 1e9,
+            "layer_7b_shape_ms": t_layer * 1e3}
 
 
 def run_reference_arm(args, cfg, rank, world):
+    """Whole tokens on the CPU; the printed `steps` is the number of tokens actually decoded (ms_per_step x steps is the
+    timed wall-clock)."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    run_layer, run_cls, cls_rows = cpu_layer_sampler(cfg, threads)
-    for _ in range(max(args.warmup, 1) if args.warmup < 3 else 3):
-        run_layer()
-    # a step = a bounded sample of one token: `sample_layers` layers' mat-vecs, scaled to all layers + classifier
-    t0 = time.perf_counter()
-    run_cls()
-    t_cls = (time.perf_counter() - t0) * cfg["vocabSize"] / cls_rows
-    budget_s = 150.0
-    times = []
-    start = time.perf_counter()
-    for _ in range(args.steps):
-        t0 = time.perf_counter()
-        run_layer()
-        times.append(time.perf_counter() - t0)
-        if time.perf_counter() - start > budget_s:
-            break
-    t_layer = float(np.mean(times))
-    ms_token = (cfg["numLayers"] * t_layer + t_cls) * 1e3
+    # a 13B-shape token takes tens of seconds on a few cores: run what fits a few minutes, at least one token
+    times, t_build = cpu_whole_tokens(cfg, threads, max_tokens=max(1, args.steps), budget_s=150.0, warm_tokens=0)
+    ms_token = float(np.mean(times)) * 1e3
     value = 1e3 / ms_token
-    sample = "per step: the 7 int4 mat-vecs + 2 RMSNorms of one layer (C# reference arithmetic: unpack to fp16, fp32 dot), " \
-             "x%d layers + classifier (timed on %d of %d rows) = one token; %d of %d steps run" % (
-                 cfg["numLayers"], cls_rows, cfg["vocabSize"], len(times), args.steps)
+    sample = ("%d whole token(s) of the %s shape through the oracle's Transformer.Forward composition in the C# reference "
+              "arithmetic (unpack every weight to fp16, sequential fp32 dot), %d threads over output rows; model built in "
+              "%.0f s (not timed); no warm-up token (each costs as much as a timed one)" % (len(times), args.config, threads, t_build))
     line = {
         "impl": "reference", "metric": "decode tokens/s batch-1", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": len(times), "warmup": args.warmup, "ms_per_step": ms_token, "higher_is_better": True, "scaling": "strong",
+        "steps": len(times), "warmup": 0, "ms_per_step": ms_token, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "llama2-%s-shape AWQ int4 g128 batch-1 greedy decode, CPU reference arithmetic" % args.config},
+        "config": config_block(args, cfg, max(1, args.gpus)),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -197,6 +234,75 @@ def run_reference_arm(args, cfg, rank, world):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+def time_matvec_single(ctx, torch, ml2, peak, peak_kind):
+    """One int4 mat-vec alone (4096 -> 4096, residual epilogue), over 32 distinct weight sets (279 MB, more than twice
+    the L2) visited in rotation: as independent launches and as a chain with programmatic dependent launch; then the
+    mat-vec set of one 7B-shape layer per round over 8 distinct layers (841 MB)."""
+    rng = np.random.default_rng(3)
+    d, h = 4096, 11008
+
+    def dev_qw(rows, cols):
+        nw, nz, ns = (-(-rows // 32)) * 4, -(-(-(-rows // 128)) // 8), -(-rows // 128)
+        w = torch.randint(0, 1 << 31, (cols * nw,), dtype=torch.int32, device="cuda")
+        z = torch.randint(0, 1 << 31, (cols * nz,), dtype=torch.int32, device="cuda")
+        s = (0.001 + 0.019 * torch.rand(cols * ns, device="cuda")).to(torch.float16)
+        return ml2.QWeight(w, z, s)
+
+    x = torch.from_numpy(rng.standard_normal(d).astype(np.float16)).cuda()
+    hv = torch.from_numpy((rng.standard_normal(h) * 0.1).astype(np.float16)).cuda()
+    outs = [torch.zeros(d, dtype=torch.float16, device="cuda") for _ in range(2)]
+    sets = [dev_qw(d, d) for _ in range(32)]
+    mv = ml2.MatVecResidual(ctx)
+    out = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, pdl in (("independent_launches", False), ("pdl_chain", True)):
+        ctx.set_pdl(pdl)
+        for q in sets:                       # warm-up round
+            mv.Forward(outs[0], x, q, d, d)
+        ctx.synchronize()
+        rounds = 6
+        e0.record()
+        for _ in range(rounds):
+            for q in sets:
+                mv.Forward(outs[0], x, q, d, d)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (rounds * len(sets))
+        b = qweight_bytes(d, d) + 2 * d + 2 * 2 * d
+        out[name] = {"us_per_matvec": us, "GB/s": b / us * 1e-3, "frac_of_8TBps": b / us * 1e-3 / 8000.0,
+                     "frac_of_%s_peak" % peak_kind: b / us * 1e-3 / peak}
+    # one 7B-shape layer's mat-vec set per round
+    layers = [dict(q=dev_qw(d, d), k=dev_qw(d, d), v=dev_qw(d, d), o=dev_qw(d, d), g=dev_qw(d, h), u=dev_qw(d, h), dn=dev_qw(h, d))
+              for _ in range(8)]
+    cfg1 = ml2.Config(dim=d, hiddenDim=h, numLayers=1, numHeads=32, numKVHeads=32, vocabSize=32, seqLength=4)
+    qkv, sw = ml2.QKVMatVec(ctx, cfg1), ml2.MatVecSwiGLU(ctx)
+    qo, ko, vo = (torch.zeros(d * 4, dtype=torch.float16, device="cuda") for _ in range(3))
+    hout = torch.zeros(h, dtype=torch.float16, device="cuda")
+
+    def layer_set(L):
+        qkv.Forward(qo, ko, vo, x, L["q"], L["k"], L["v"], d, d, 0, 0)
+        mv.Forward(outs[0], x, L["o"], d, d)
+        sw.Forward(hout, x, L["g"], L["u"], d, h)
+        mv.Forward(outs[1], hv, L["dn"], h, d)
+    for L in layers:
+        layer_set(L)
+    ctx.synchronize()
+    e0.record()
+    for _ in range(4):
+        for L in layers:
+            layer_set(L)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (4 * len(layers))
+    b = 4 * qweight_bytes(d, d) + 2 * qweight_bytes(d, h) + qweight_bytes(h, d)
+    out["layer_7b_shape_pdl_chain"] = {"us_per_layer_set": us, "GB/s": b / us * 1e-3, "frac_of_8TBps": b / us * 1e-3 / 8000.0,
+                                       "frac_of_%s_peak" % peak_kind: b / us * 1e-3 / peak}
+    ctx.set_pdl(False)
+    out["how"] = ("ml2_matvec_residual_int4 / ml2_qkv_matvec_int4 / ml2_matvec_swiglu_int4 (stream_matvec_kernel), CUDA events on "
+                  "the context's stream, distinct weights every launch (working set far larger than L2)")
+    return out
+
+
 def run_gpu_arm(args, cfg, rank, world, local_rank):
     import torch
     import managedllama2_b200 as ml2
@@ -214,13 +320,64 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             idt = torch.frombuffer(bytearray(ml2.Transformer.nccl_unique_id()), dtype=torch.uint8).cuda()
         dist.broadcast(idt, 0)
         nccl_id = bytes(idt.cpu().numpy().tobytes())
-
-    seq_len = max(PROMPT_LEN, args.context) + args.warmup + 2 * args.steps + 8
-    config = ml2.Config(seqLength=seq_len, **cfg)
+    fused = os.environ.get("ML2_TP_FUSED", "1") == "1"
     ctx = ml2.CudaContext(local_rank)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- correctness of the sharded path before anything is timed (N > 1): 2 layers of the same shape -------------
+    tp_check = None
+    if world > 1:
+        import oracle
+        c2 = dict(cfg)
+        c2["numLayers"] = 2
+        conf2 = ml2.Config(seqLength=16, **c2)
+        w2 = ml2.synthetic_weights(ctx, conf2, seed=SEED + 1, tp_size=world, tp_rank=rank, sigma=1.0)
+        t2 = ml2.Transformer(conf2, w2, ctx, tp_size=world, tp_rank=rank, nccl_id=nccl_id)
+        if fused:
+            t2.attach_peers_with(dist)
+        toks = [11, 4242, 31999 % conf2.vocabSize, 77]
+        t2.set_tokens(np.array(toks, dtype=np.int32))
+        cpu = None
+        if rank == 0:
+            oracle.set_threads(os.cpu_count() or 1)
+            cpu = oracle.CpuModel(oracle_cfg(c2, 16), ml2.synthetic_weights_host(conf2, seed=SEED + 1, sigma=1.0), mode=1)
+        identical, max_err, ok = True, 0.0, True
+        for pos in range(4):
+            t2.Forward(pos, pos + 1, False)
+            lg = t2.logits()
+            t = torch.from_numpy(lg.view(np.int16).astype(np.int32)).cuda()
+            lo, hi = t.clone(), t.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            identical = identical and bool((lo == hi).all().item())
+            if rank == 0:
+                want = cpu.forward(toks[pos], pos).astype(np.float32)
+                err = float(np.abs(lg.astype(np.float32) - want).max())
+                max_err = max(max_err, err / max(float(want.std()), 1e-9))
+        ok = identical and max_err <= 2e-2 and ctx.status() == (0, 0)
+        tp_check = {"max_err_over_logit_std": max_err, "rank_identical": identical, "ok": bool(ok),
+                    "what": "2-layer cut of the timed shape, unit-scale weights, 4 tokens, logits vs the CPU oracle of the unsharded model"}
+        t2.close()
+        del w2
+        torch.cuda.empty_cache()
+
+    seq_len = LONG_PROMPT + LONG_STEPS + 8 if not args.no_long else PROMPT_LEN + args.warmup + 2 * args.steps + 8
+    seq_len = max(seq_len, max(PROMPT_LEN, args.context) + args.warmup + 2 * args.steps + 8)
+    config = ml2.Config(seqLength=seq_len, **cfg)
     weights = ml2.synthetic_weights(ctx, config, seed=SEED, tp_size=world, tp_rank=rank)
     tr = ml2.Transformer(config, weights, ctx, tp_size=world, tp_rank=rank, nccl_id=nccl_id)
-    if dist is not None and os.environ.get("ML2_TP_FUSED", "1") == "1":
+    if dist is not None and fused:
         tr.attach_peers_with(dist)   # persistent kernel per GPU, all-reduce fused over peer memory
     sp = ctypes.c_void_p()
     _lib.check(tr.lib.ml2_model_stream(tr.handle, ctypes.byref(sp)))
@@ -230,20 +387,18 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     prompt = rng.integers(3, config.vocabSize, size=PROMPT_LEN).astype(np.int32)
     tr.set_tokens(prompt)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # prompt (token by token, as the reference does) + warm-up decode steps
+    # prompt (token by token, as the reference does: src/Transformer.cs:96-104) + warm-up decode steps
     pos = 0
     for _ in range(PROMPT_LEN - 1):
         tr.Forward(pos, pos + 1, False)
         pos += 1
     if args.context > pos:
-        # long-context timing aid (BASELINE configs[4]): continue from position `context`; the cache rows in between hold
-        # whatever the allocation held, the attention still reads and weighs all of them
-        pos = args.context
+        # profiling aid only: prefill up to `context` token by token with seeded ids
+        filler = rng.integers(3, config.vocabSize, size=args.context + 1).astype(np.int32)
+        tr.set_tokens(filler[pos + 1:args.context + 1], first=pos + 1)
+        while pos < args.context:
+            tr.Forward(pos, pos + 1, False)
+            pos += 1
     for _ in range(args.warmup):
         tr.Forward(pos, pos + 1, True)
         pos += 1
@@ -258,6 +413,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = ctx.launch_count
+    first_timed = pos
     e0.record(stream)
     for _ in range(args.steps):
         tr.Forward(pos, pos + 1, True)
@@ -266,11 +422,10 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     tr.synchronize()
     barrier()
     launches = ctx.launch_count - launches0
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    # the greedy token ids of the timed steps (identical on every rank and for every N if the sharded path is right)
+    ids = [tr.read_token(p) for p in range(first_timed + 1, first_timed + 1 + min(args.steps, 64))]
+    token_hash = hashlib.sha256(np.array(ids, dtype=np.int32).tobytes()).hexdigest()[:16]
 
     # ---- end to end: host-driven loop, token id in (pinned, 4 B) and sampled id out (4 B) per step ----
     pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -286,19 +441,51 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         pos += 1
         tok = out_tok.value
     torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
     clocks = sampler.stop() if rank == 0 else None
+    short_mid = first_timed + args.steps // 2          # mean position of the device-timed region
 
-    # ---- per-operator kernels timed alone (every kernel's achieved GB/s) -------------------------------
+    # ---- long context: a 4032-token prompt prefilled token by token, then 64 decode steps up to position 4096 ------
+    long_ctx = None
+    if not args.no_long and args.context == 0:
+        lp = rng.integers(3, config.vocabSize, size=LONG_PROMPT).astype(np.int32)
+        tr.set_tokens(lp)
+        p2 = 0
+        t0 = time.perf_counter()
+        for _ in range(LONG_PROMPT - 1):
+            tr.Forward(p2, p2 + 1, False)
+            p2 += 1
+        tr.synchronize()
+        prefill_s = time.perf_counter() - t0
+        for _ in range(3):                      # warm-up at this length (generated tokens continue the prompt)
+            tr.Forward(p2, p2 + 1, True)
+            p2 += 1
+        barrier()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_long = LONG_STEPS - 4
+        l0.record(stream)
+        for _ in range(n_long):
+            tr.Forward(p2, p2 + 1, True)
+            p2 += 1
+        l1.record(stream)
+        tr.synchronize()
+        barrier()
+        lms = max_over_ranks(l0.elapsed_time(l1)) / n_long
+        mid = p2 - n_long // 2
+        kvb = cfg["numLayers"] * 2 * (mid + 1) * (cfg["dim"] // world) * 2
+        lb = token_bytes(cfg, world) + kvb
+        peak, peak_kind = measured_peak_gbs()
+        long_ctx = {"tokens/s": 1e3 / lms, "ms_per_step": lms, "steps": n_long, "positions": [p2 - n_long, p2 - 1],
+                    "prefill": "%d prompt tokens, one forward each (%.1f s)" % (LONG_PROMPT, prefill_s),
+                    "algorithmic_bytes_per_launch": lb, "kv_cache_bytes_read_per_launch": kvb,
+                    "roofline_frac": lb / (lms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind}
+
+    # ---- per-operator kernels timed alone (graph-path kernels; every kernel's achieved GB/s) ------------------------
+    tr.Forward(short_mid, short_mid + 1, False)       # the attention kernel is timed at the bench's mean position
     avg_us = (ctypes.c_double * 6)()
     nbytes = (ctypes.c_double * 6)()
     _lib.check(tr.lib.ml2_model_profile(tr.handle, 5, avg_us, nbytes))
     status = ctx.status()
-    final_pos = pos
 
     # ---- the reference's own CUDA kernels on the same weights (one GPU only) ----------------------------
     ref_cuda = None
@@ -336,8 +523,13 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                             "launches_per_token": 10 * config.numLayers + 4, "position": rpos,
                             "how": "reference native/*.cu compiled unmodified for sm_100a, launch shapes of src/*.cs, "
                                    "Transformer.Forward order; graph replay removes host launch overhead"}
-        except Exception as e:  # the reference arm is informative only
+        except Exception as e:  # this leg is informative only
             ref_cuda = {"unavailable": repr(e)[:200]}
+
+    persistent = tr.launches_per_token == 1
+    tr.close()
+    del weights
+    torch.cuda.empty_cache()
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -345,13 +537,19 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         kernels = {n: {"us": avg_us[i], "GB/s": nbytes[i] / avg_us[i] * 1e-3, "bytes": nbytes[i],
                        "frac_of_%s_peak" % peak_kind: nbytes[i] / avg_us[i] * 1e-3 / peak,
                        "frac_of_8TBps": nbytes[i] / avg_us[i] * 1e-3 / 8000.0} for i, n in enumerate(names)}
+        kernels["how"] = ("the per-operator kernels of the CUDA-graph path, swept over all layers (distinct weights every launch), "
+                          "chained with programmatic dependent launch as that path runs them; attention at position %d" % short_mid)
+        matvec_single = None
+        if world == 1:
+            try:
+                matvec_single = time_matvec_single(ctx, torch, ml2, peak, peak_kind)
+            except Exception as e:
+                matvec_single = {"unavailable": repr(e)[:200]}
         tokens_per_s = args.steps / ms * 1e3
         tb = token_bytes(cfg, world)
-        persistent = tr.launches_per_token == 1
         if persistent:
             # one persistent kernel per token: it is the dominant (only) kernel; its launch duration is the step time
-            mid = final_pos - args.steps - args.steps // 2          # mean position of the device-timed region
-            kv = cfg["numLayers"] * 2 * (mid + 1) * (cfg["dim"] // world) * 2
+            kv = cfg["numLayers"] * 2 * (short_mid + 1) * (cfg["dim"] // world) * 2
             dom_name = "decode_token_kernel (persistent, whole token)"
             dom_bytes = tb + kv
             achieved = dom_bytes / (ms / args.steps * 1e-3) / 1e9
@@ -360,23 +558,22 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             dom_name = "stream_matvec_kernel<Int4,SwiGLU,RMSNorm> (gate/up)"
             dom_bytes = nbytes[dom]
             achieved = nbytes[dom] / avg_us[dom] * 1e-3
+        ratio = profiled_traffic_ratio() if persistent else None
         threads = os.cpu_count() or 1
+        cpu_baseline = None
         if world == 1 and not args.no_cpu:
-            cpu_val, t_layer, t_cls = cpu_tokens_per_s(cfg, threads, 3)
-            cpu_baseline = {"value": cpu_val, "unit": "tokens/s", "cores": threads, "kind": "port",
-                            "sample": "3 repetitions of one layer's 7 int4 mat-vecs (C# reference arithmetic) x %d layers + "
-                                      "classifier slice scaled to %d rows" % (cfg["numLayers"], cfg["vocabSize"])}
-        else:
-            cpu_baseline = None
+            # whole tokens of the timed shape on all cores (one token is 10-30 s of CPU work), plus the one-thread small cases
+            times, t_build = cpu_whole_tokens(cfg, threads, max_tokens=1, budget_s=30.0)
+            cpu_baseline = {"value": 1.0 / float(np.mean(times)), "unit": "tokens/s", "cores": threads, "kind": "port",
+                            "sample": "%d whole token(s) of the %s shape, C# reference arithmetic (unpack to fp16, sequential fp32 dot), "
+                                      "%d threads over output rows; %.1f s per token" % (len(times), args.config, threads, float(np.mean(times))),
+                            "single_thread": cpu_single_thread_small_cases()}
         line = {
             "metric": "decode tokens/s batch-1", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "llama2-%s-shape%s AWQ int4 g128, batch-1 greedy decode, %d-token prompt then decode" %
-                                   (args.config, (" cut to %d layers" % args.layers) if args.layers else "", PROMPT_LEN) +
-                                   ((" from position %d" % args.context) if args.context else ""),
-                       "parallelism": "tp%d" % world, "l2": "per-token working set %.2f GB per GPU, far larger than L2" % (tb / 1e9),
-                       "bytes_per_token_per_gpu": tb},
+            "config": config_block(args, cfg, world),
+            "positions_timed": [first_timed, first_timed + args.steps - 1],
             "hbm_frac_of_token": {"achieved_GB/s": tb * tokens_per_s / 1e9, "of_%s_peak" % peak_kind: tb * tokens_per_s / 1e9 / peak,
                                   "of_8TBps": tb * tokens_per_s / 1e9 / 8000.0},
             "e2e": {"value": args.steps / e2e_ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
@@ -384,18 +581,21 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "algorithmic_bytes_per_launch": dom_bytes,
                          "frac_of_8TBps": achieved / 8000.0,
-                         # dram__bytes_read+write of one launch: ncu capture of the 8-layer case (1.6597 GB moved for
-                         # 1.6496 GB algorithmic), scaled by the bytes of this launch
-                         "traffic": (dom_bytes * 1.00612) if persistent else None,
-                         "traffic_source": "ncu dram bytes of the 8-layer capture x (bytes of this launch / bytes of that launch)"},
+                         "traffic": (dom_bytes * ratio) if ratio else None,
+                         "traffic_source": ("ncu dram bytes per algorithmic byte of the kept 8-layer capture (profiles/) x the bytes of this launch"
+                                            if ratio else "not measured in this run")},
+            "long_context": long_ctx,
+            "matvec_single": matvec_single,
             "kernels_timed_alone": kernels,
             "reference_cuda_kernels": ref_cuda,
             "cpu_baseline": cpu_baseline,
+            "tp_check": tp_check,
+            "greedy_token_hash": token_hash,
             "clocks": clocks,
             "device_status": list(status),
         }
         print(json.dumps(line), flush=True)
-    tr.close()
+    ctx.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -410,7 +610,8 @@ def main():
     ap.add_argument("--config", default="13b", choices=sorted(CONFIGS))
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the shape with fewer layers (smaller device footprint)")
     ap.add_argument("--no-cpu", action="store_true", help="profiling aid: skip the CPU baseline leg")
-    ap.add_argument("--context", type=int, default=0, help="profiling aid: time the decode steps from this position on (long-context case)")
+    ap.add_argument("--no-long", action="store_true", help="profiling aid: skip the long-context leg")
+    ap.add_argument("--context", type=int, default=0, help="profiling aid: prefill to this position (token by token) before the timed steps")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

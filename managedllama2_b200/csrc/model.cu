@@ -341,6 +341,8 @@ static int enqueue_token(Model* m, int pos, int next_pos, int write_token)
 
 // Launches one kernel kind of one layer exactly as the token sequence does (no NCCL, no PDL); used by the
 // profiler below. kind: 0 qkv, 1 attention, 2 o-proj, 3 gate/up, 4 down, 5 classifier.
+// One kernel of the CUDA-graph path on its own (ml2_model_profile), chained to its predecessor with programmatic
+// dependent launch as the token's graph chains them: the weight prefetch of a launch overlaps the tail of the one before.
 static int enqueue_kind(Model* m, int kind, int l)
 {
     Ctx* ctx = m->ctx;
@@ -361,7 +363,7 @@ static int enqueue_kind(Model* m, int kind, int l)
         p.in = m->x; p.gamma = L.rms_att; p.eps = m->eps;
         p.rope_table = m->rope_table; p.pos_ptr = &m->step->pos; p.kv_row_stride = m->dim_local;
         p.rows = dim; p.cols = m->dim_local; p.nmat = 3; p.head_size = m->head_size;
-        return launch_matvec(ctx, Fmt::Int4, Epi::QKVRope, Pro::RMSNorm, pl, p, false);
+        return launch_matvec(ctx, Fmt::Int4, Epi::QKVRope, Pro::RMSNorm, pl, p, m->use_pdl);
     case 1: {
         AttnParams a{};
         const int chunk_cap = std::max(ceil_div(c.seq_len, kAttnCluster), kAttnSingleCtaMax);
@@ -382,21 +384,21 @@ static int enqueue_kind(Model* m, int kind, int l)
         if ((rc = plan_matvec(ctx, Fmt::Int4, e, rows, dim, 1, &pl))) return rc;
         p.mat[0] = qwp(kind == 2 ? L.o : L.down); p.in = kind == 2 ? m->xb : m->h; p.rows = rows; p.cols = dim; p.nmat = 1;
         p.out[0] = m->x; p.out_f32 = m->partial;
-        return launch_matvec(ctx, Fmt::Int4, e, Pro::Plain, pl, p, false);
+        return launch_matvec(ctx, Fmt::Int4, e, Pro::Plain, pl, p, m->use_pdl);
     }
     case 3:
         if ((rc = plan_matvec(ctx, Fmt::Int4, Epi::SwiGLU, dim, m->hidden_local, 2, &pl))) return rc;
         p.mat[0] = qwp(L.gate); p.mat[1] = qwp(L.up); p.out[0] = m->h;
         p.in = m->x; p.gamma = L.rms_ffn; p.eps = m->eps;
         p.rows = dim; p.cols = m->hidden_local; p.nmat = 2;
-        return launch_matvec(ctx, Fmt::Int4, Epi::SwiGLU, Pro::RMSNorm, pl, p, false);
+        return launch_matvec(ctx, Fmt::Int4, Epi::SwiGLU, Pro::RMSNorm, pl, p, m->use_pdl);
     case 5:
         if ((rc = plan_matvec(ctx, Fmt::F16, Epi::Store, dim, m->vocab_local, 1, &pl))) return rc;
         p.mat[0] = QWPtrs{reinterpret_cast<const uint32_t*>(m->classifier), nullptr, nullptr};
         p.out[0] = m->tp > 1 ? m->logits_local : m->logits;
         p.in = m->x; p.gamma = m->rms_final; p.eps = m->eps;
         p.rows = dim; p.cols = m->vocab_local; p.nmat = 1;
-        return launch_matvec(ctx, Fmt::F16, Epi::Store, Pro::RMSNorm, pl, p, false);
+        return launch_matvec(ctx, Fmt::F16, Epi::Store, Pro::RMSNorm, pl, p, m->use_pdl);
     }
     return fail(ML2_E_INVALID, "profile: kind %d", kind);
 }

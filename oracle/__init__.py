@@ -368,3 +368,32 @@ def awq_pack_v0(values, height, width):
     for j in range(8):
         out |= (v[:, :, AWQ_ORDER_MAP[j]] & np.uint32(0xF)) << np.uint32(4 * j)
     return out.reshape(-1)
+
+
+# ---- synthetic model of the benchmark's value distributions (numpy only) ---------------------------------------------
+
+def synthetic_weights(cfg, seed=31415, sigma=0.02):
+    """A model of the benchmark construction made with numpy alone (the CPU arm of the benchmark must not need the
+    product library): int4 nibbles and zero points uniform in [0, 15], group scales uniform in [0.001, 0.02],
+    embeddings / classifier / norm weights ~ N(0, sigma^2), in the QWeight layout of src/QWeight.cs:5-10 with the
+    per-row sizes of src/TransformerWeights.cs:54-69. The values are not those of the device generator (nor need they
+    be: the arm is timed, not compared)."""
+    rng = np.random.default_rng(seed)
+    dim, hid, vocab = cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"]
+
+    def qweight(rows, cols):
+        nw, nz, ns = qweight_sizes(rows)
+        w = rng.integers(0, 1 << 32, size=cols * nw, dtype=np.uint32)
+        z = rng.integers(0, 1 << 32, size=cols * nz, dtype=np.uint32)
+        s = (0.001 + 0.019 * rng.random(cols * ns, dtype=np.float32)).astype(np.float16)
+        return w, z, s
+
+    def normal(n):
+        return (rng.standard_normal(n, dtype=np.float32) * sigma).astype(np.float16)
+
+    out = {"embed": normal(vocab * dim), "classifier": normal(vocab * dim), "rms_final": normal(dim), "layers": []}
+    for _ in range(cfg["n_layers"]):
+        out["layers"].append({"q": qweight(dim, dim), "k": qweight(dim, dim), "v": qweight(dim, dim), "o": qweight(dim, dim),
+                              "gate": qweight(dim, hid), "up": qweight(dim, hid), "down": qweight(hid, dim),
+                              "rms_att": normal(dim), "rms_ffn": normal(dim)})
+    return out
