@@ -2,24 +2,24 @@
 // (src/Transformer.cs:158-190 of GilesBathgate/ManagedLlama2) runs inside a single cooperative launch with
 // one CTA per SM, so HBM streaming never stops at an operator boundary.
 //
-//   * producer warp   walks the token's operator list and streams every weight tile this CTA owns, operator
-//                     after operator, into one shared-memory ring (1-D bulk async copies, mbarrier completion).
-//                     Weights do not depend on activations, so it runs ahead of the arithmetic by the depth of
-//                     the ring, across operator boundaries.
 //   * rows            every operator's output rows are cut into contiguous, balanced ranges, one per CTA; a CTA
-//                     streams its range as tiles of up to `rmax` rows (three copies per tile: packed weights, zero
-//                     words, scales). Tile sizes are spread evenly over the range, so all CTAs run the same number
-//                     of arithmetic steps.
-//   * consumer warps  work in groups of `kw` warps (one group spans a whole weight row: a lane owns one or two
-//                     16-byte weight vectors of every row, its inputs stationary in registers). ALL groups share a
-//                     tile: group g takes rows g, g + G, ... of it. A group sums its k-warps through shared memory
-//                     behind a named barrier and its first warp runs the operator's tail (residual add, SwiGLU,
-//                     stores) with the reference's fp16 rounding points. No separate finalizer warps.
-//   * hand-off        when a CTA has stored its share of an operator, ONE thread publishes it (release) on the
-//                     operator's device-wide counter; the next operator starts when the counter is complete
-//                     (acquire by one thread, CTA barrier), builds its prepared input table cooperatively
-//                     (RMSNorm applied where the reference runs rmsnorm first) and goes on with tiles that the
-//                     producer has already brought in.
+//                     streams its range as tiles of up to `rmax` rows (packed weights, zero words, scales). The host
+//                     works this out once per model and leaves every CTA a flat list of tile descriptors (sources,
+//                     sizes and shared-memory offsets of the tile's copies; first row, rows, operator, output).
+//   * copy warp       walks the CTA's tile list and streams every tile, operator after operator, into one shared-memory
+//                     ring (1-D bulk async copies, mbarrier completion). Weights do not depend on activations, so it
+//                     runs ahead of the arithmetic by the depth of the ring, across operator boundaries.
+//   * consumer warps  int4 operators: every warp takes one or two quantisation groups (128 inputs) of ALL rows of a
+//                     tile on the tensor cores (warp-wide m16n8k16 steps on nibbles unpacked in registers, its inputs
+//                     stationary in registers as B fragments) and leaves one partial sum per row in shared memory.
+//                     fp16 operator (classifier): groups of `kw` warps span a row, group g takes rows g, g + G, ...
+//   * tail warp       when all consumer warps have arrived on a slot's barrier, adds the warps' partial sums of the
+//                     tile in a fixed order and runs the operator's tail (residual add, SwiGLU, stores) with the
+//                     reference's fp16 rounding points; after the CTA's last tile of an operator it publishes the
+//                     operator (release) on its device-wide counter.
+//   * hand-off        the next operator starts when the counter is complete (acquire by one thread, CTA barrier),
+//                     builds its prepared input table cooperatively (RMSNorm applied where the reference runs rmsnorm
+//                     first) and goes on with tiles that the copy warp has already brought in.
 //   * attention       is an operator without weights, with the steps and rounding points of the reference's
 //                     rope / scores / softmax / values kernels: one CTA per head for short contexts, several CTAs
 //                     per head (parts of the sequence, maximum / exp-sum exchanged through global memory) for long
@@ -44,14 +44,15 @@ struct MegaOp {
     int paired;              // 1: a unit of work is row i of mat[0] together with row i of mat[1] (SwiGLU)
     int wrow, zrow, srow;    // bytes of one output row in the weight / zero / scale arrays (fp16 weights: 2 * rows, 0, 0)
     int units;               // 16-byte weight vectors (lane slots) per row
-    int kw, groups, np;      // warps per group, groups per CTA, weight vectors per lane and row (1 or 2)
+    int kw, groups, np;      // fp16 weights: warps per group, groups per CTA, weight vectors per lane and row (1 or 2)
+                             // int4 weights: working warps, 1, quantisation groups per warp
+    int ngrp, tab_n, two;    // int4: quantisation groups per row; lane slots of the input table; a tile has a second block of 8 rows
     int gran;                // rows per alignment granule: every tile is a whole number of granules
     int rmax;                // units (rows, or row pairs) of a full tile
     int off_z, off_s, run_bytes;   // shared-memory layout of one run (the rows of one matrix in a tile)
     int has_tiles;           // weight operator
     int rot, seg_rot;        // rotation of the CTA -> row range assignment, per operator and per segment
     int ngran, gmax;         // granules of a segment (cols / gran), granules of a full tile (rmax / gran)
-    float inv_ncta, inv_gmax;   // reciprocals used by the tile arithmetic (1 / CTAs of the launch, 1 / gmax)
     int tp;                  // ranks summed into the input (pro 3) / receiving the output (MOP_PARTIAL, sharded MOP_CLS)
     int out_row0;            // sharded classifier: first vocabulary row of this rank
     int att_layer;           // layer index (the split-attention counters advance once per layer and token)
@@ -73,9 +74,32 @@ struct MegaOp {
     unsigned int* att_cnt;   // [heads]: arrivals of the parts, monotonically increasing
 };
 
+// One tile of one CTA: everything the copy warp and the tail warp need, worked out by the host (128 bytes).
+struct MegaTileCopy {
+    const void* src;          // 16-byte aligned
+    uint32_t bytes;           // multiple of 16; 0: unused entry
+    uint32_t dst;             // byte offset inside the ring slot
+};
+struct MegaTile {
+    MegaTileCopy cp[6];       // weights, zero words, scales of the tile's one or two runs
+    int row, n;               // first unit (row, or gate / up row pair) and units
+    uint32_t info;            // bits 0..15 operator index, 16..17 segment, 18: the CTA's last tile of the operator,
+                              // 19: the output row is the cache row of the token's position (k and v)
+    uint32_t total_bytes;     // sum over cp
+    __half* out;              // output vector of the tile's segment
+    uint32_t opbits;          // bits 0..2 operator kind, 3 paired, 4 int4 (tensor-core partial layout), 5 the operator's counter
+                              // lives on every rank, 8..15 kw, 16..23 groups
+    uint32_t pad;
+};
+static_assert(sizeof(MegaTile) == 128, "tile descriptor");
+constexpr uint32_t kTileLast = 1u << 18, kTileCacheRow = 1u << 19;
+
 struct MegaParams {
     const MegaOp* ops;
     int nops;
+    const MegaTile* tiles;     // every CTA's tiles in the order it streams them
+    const int* tile_begin;     // [gridDim.x + 1] offsets into `tiles`
+    const unsigned short* op_tiles;   // [nops][gridDim.x] tiles of each operator on each CTA
     unsigned int* done;        // [nops] arrivals, monotonically increasing over tokens
     DeviceStatus* status;
     const float2* rope_table;
@@ -96,12 +120,16 @@ struct MegaParams {
 };
 
 constexpr int kMegaConsumerWarps = 21;   // 4 groups of 5, 3 of 7, 5 of 4, 2 of 10
-constexpr int kMegaWarps = kMegaConsumerWarps + 2;   // + copy warp + tail warp
+constexpr int kMegaServiceWarps = 2;     // copy warp and tail warp: the CTA's FIRST warps (the scheduler favours low warp numbers, and
+                                         // these two issue little but sit on every tile's critical path)
+constexpr int kMegaServiceThreads = kMegaServiceWarps * 32;
+constexpr int kMegaWarps = kMegaConsumerWarps + kMegaServiceWarps;
 constexpr int kMegaThreads = kMegaWarps * 32;
 constexpr int kMegaConsThreads = kMegaConsumerWarps * 32;
 constexpr int kMegaMaxStages = 6;
 constexpr int kMegaMaxGroups = 8;     // named barriers 2 .. 9
-constexpr int kMegaGroupRows = 8;     // physical rows of one tile that one group may own
+constexpr int kMegaGroupRows = 8;     // physical rows of one tile that one group may own (fp16 weights)
+constexpr int kMegaRedRows = 16;      // partial sums one warp may leave per tile
 constexpr int kMegaRedBufs = 8;       // tiles whose k-warp partials may be waiting for their tail (more than the ring depth + 1)
 constexpr int kMegaMaxSplit = 8;      // CTAs per head of the split attention
 constexpr int kAttUnroll = 8;         // cache rows a warp keeps in flight
@@ -206,45 +234,6 @@ __device__ __forceinline__ void mega_wait_counter(const unsigned int* counter, u
     mega_give_up(w, code, detail);
 }
 
-// ---- row ranges and tiles ------------------------------------------------------------------------------------------------
-// Segment s of an operator (matrix s of QKV; the only segment otherwise) has cols / gran granules; CTA c owns a
-// contiguous, balanced range of them, cut into tiles whose sizes differ by at most one granule.
-struct MegaSeg {
-    int row0;          // first unit of this CTA's range
-    int nt;            // tiles
-    int base, extra;   // granules per tile: base (+1 for the first `extra` tiles)
-};
-
-// x / d for 0 <= x < 2^23 and small d, without the integer-division routine (`inv_d` = 1 / d rounded to float)
-__device__ __forceinline__ int mega_div(int x, int d, float inv_d)
-{
-    int q = __float2int_rz((float)x * inv_d);
-    const int r = x - q * d;
-    q += (r >= d ? 1 : 0) - (r < 0 ? 1 : 0);
-    return q;
-}
-
-__device__ __forceinline__ MegaSeg mega_segment(const MegaOp& op, int seg, int cta, int ncta)
-{
-    MegaSeg s;
-    int c = cta + op.rot + seg * op.seg_rot;
-    c -= mega_div(c, ncta, op.inv_ncta) * ncta;
-    const int G = op.ngran;                         // granules of the segment (< 2^23 / ncta)
-    const int g0 = mega_div(c * G, ncta, op.inv_ncta), g1 = mega_div((c + 1) * G, ncta, op.inv_ncta);
-    const int ng = g1 - g0;
-    s.row0 = g0 * op.gran;
-    s.nt = mega_div(ng + op.gmax - 1, op.gmax, op.inv_gmax);   // gmax = granules of a full tile
-    s.base = 0;
-    s.extra = 0;
-    if (s.nt > 0) {
-        s.base = mega_div(ng, s.nt, __frcp_rn((float)s.nt));
-        s.extra = ng - s.base * s.nt;
-    }
-    return s;
-}
-
-__device__ __forceinline__ int mega_segments(const MegaOp& op) { return op.paired ? 1 : op.nmat; }
-
 // ---- shared-memory objects --------------------------------------------------------------------------------------------
 struct MegaShared {
     unsigned char* ring;      // nstage * slot_bytes, then the table / scratch area
@@ -254,33 +243,35 @@ struct MegaShared {
     float* red;               // [kMegaRedBufs][kMegaConsumerWarps][kMegaGroupRows]
     float* part;              // [2][kMegaConsumerWarps] sum-of-squares partials
     float* resid;             // [kMegaRedBufs][kMegaMaxGroups][kMegaGroupRows] residual values of the tiles in flight
+    const int* tile_row;      // [nstage] first unit of the tile in each slot ...
+    const int* tile_n;        // ... and its units (written by the copy warp before the slot's copies)
 };
 
 // ---- prepared input table ---------------------------------------------------------------------------------------------
 // int4 operators: lane slot u (32 consecutive inputs = one 16-byte weight vector of every row, one quarter of a
-// quantisation group) owns five 16-byte vectors, stored as table[q * tab_n + u]:
-//   q = 0..3   the inputs of packed word q as fp16 pairs (x0,x4) (x1,x5) (x2,x6) (x3,x7)   (see word_dot)
-//   q = 4      accumulator start values -1024 * S(even inputs), -1024 * S(odd inputs), and the sum of the inputs
-//              of the slot's whole quantisation group (zero-point term)
+// quantisation group) owns four 16-byte vectors, stored as table[q * tab_n + u]:
+//   q = 0..3   the inputs of packed word q as fp16 pairs (x0,x4) (x1,x5) (x2,x6) (x3,x7): the B fragments of the two
+//              tensor-core steps that consume the word (see mega_mma_word)
+// and every quantisation group G one more, table[4 * tab_n + G]:
+//   .x  -(1024 * S(inputs under even nibbles) + 64 * S(inputs under odd nibbles)): start value of the accumulator, it
+//       removes the exponent offsets of the unpacked nibbles;   .y  S(all inputs of the group): zero-point term
 // fp16 operators: table[u] = the 8 inputs of slot u.
 // Slots past the end of the row hold zeros.
 __device__ __forceinline__ void mega_table_store_int4(uint4* tab, int tab_n, int i, uint4 t)
 {
-    // thread i holds inputs [8i, 8i + 8): word (i & 3) of slot (i >> 2); the four threads of a slot are adjacent lanes
+    // thread i holds inputs [8i, 8i + 8): word (i & 3) of slot (i >> 2); the 16 threads of a group are adjacent lanes
     const uint32_t x0 = __byte_perm(t.x, t.z, 0x5410), x1 = __byte_perm(t.x, t.z, 0x7632);
     const uint32_t x2 = __byte_perm(t.y, t.w, 0x5410), x3 = __byte_perm(t.y, t.w, 0x7632);
     float ev = half_bits_to_float(lo16(t.x)) + half_bits_to_float(lo16(t.y)) + half_bits_to_float(lo16(t.z)) + half_bits_to_float(lo16(t.w));
     float od = half_bits_to_float(hi16(t.x)) + half_bits_to_float(hi16(t.y)) + half_bits_to_float(hi16(t.z)) + half_bits_to_float(hi16(t.w));
-    ev += __shfl_xor_sync(0xffffffffu, ev, 1);
-    od += __shfl_xor_sync(0xffffffffu, od, 1);
-    ev += __shfl_xor_sync(0xffffffffu, ev, 2);
-    od += __shfl_xor_sync(0xffffffffu, od, 2);
-    float grp = ev + od;
-    grp += __shfl_xor_sync(0xffffffffu, grp, 4);
-    grp += __shfl_xor_sync(0xffffffffu, grp, 8);
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+        ev += __shfl_xor_sync(0xffffffffu, ev, o);
+        od += __shfl_xor_sync(0xffffffffu, od, o);
+    }
     const int u = i >> 2, q = i & 3;
     tab[q * tab_n + u] = make_uint4(x0, x1, x2, x3);
-    if (q == 0) tab[4 * tab_n + u] = make_uint4(__float_as_uint(-1024.f * ev), __float_as_uint(-1024.f * od), __float_as_uint(grp), 0u);
+    if ((i & 15) == 0) tab[4 * tab_n + (i >> 4)] = make_uint4(__float_as_uint(-(1024.f * ev + 64.f * od)), __float_as_uint(ev + od), 0u, 0u);
 }
 
 struct MegaSlice {
@@ -446,16 +437,25 @@ __device__ __forceinline__ void mega_ring_next(MegaRing& r, int nstage)
     if (++r.slot == nstage) { r.slot = 0; r.parity ^= 1u; }
 }
 
+// a consumer warp that has no part in an operator's tiles (nor in their barriers) only keeps its ring position in step
+__device__ __forceinline__ void mega_skip_tiles(MegaRing& rp, uint32_t& tile_no, int tiles, int nstage)
+{
+    tile_no += (uint32_t)tiles;
+    const int pos = rp.slot + tiles;
+    const int wraps = pos / nstage;
+    rp.slot = pos - wraps * nstage;
+    rp.parity ^= (uint32_t)wraps & 1u;
+}
+
 // ---- consumer side of one weight operator ---------------------------------------------------------------------------
 // Everything that does not change from tile to tile is worked out once per operator; a tile costs a wait, the batches,
 // an arrival, the group's barrier and (first warp of the group) the tail.
 template <bool INT4, int NP, bool kProf>
 __device__ __forceinline__ void mega_consume(const MegaOp* __restrict__ gp, const MegaParams& p, int k, const MegaShared& sh, MegaRing& rp,
-                                             uint32_t& tile_no, const MegaWait& w, long long& t_full, long long& t_batch)
+                                             uint32_t& tile_no, const MegaWait& w, int my_tiles, long long& t_full, long long& t_batch)
 {
     constexpr int NR = 4 / NP;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int ncta = gridDim.x, cta = blockIdx.x;
+    const int tid = (int)threadIdx.x - kMegaServiceThreads, lane = tid & 31, warp = tid >> 5;
     const int G = gp->groups, kw = gp->kw, kind = gp->kind;
     const bool paired = gp->paired != 0;
     const int group = warp / kw, kw_id = warp - group * kw;
@@ -492,162 +492,407 @@ __device__ __forceinline__ void mega_consume(const MegaOp* __restrict__ gp, cons
     const int zshift = (gj & 7) * 4;
     const bool storer = lane < 4 && (lane % NP) == 0;     // lane r * NP of quad 0 stores row r of a batch
     const int recipG = (65536 + G - 1) / G;                // x / G for the small x that occur below
-    float* const red_w = sh.red + warp * kMegaGroupRows + (lane & 3) / NP;
-    constexpr int kRedBuf = kMegaConsumerWarps * kMegaGroupRows;
+    float* const red_w = sh.red + warp * kMegaRedRows + (lane & 3) / NP;
+    constexpr int kRedBuf = kMegaConsumerWarps * kMegaRedRows;
     static_assert((kMegaRedBufs & (kMegaRedBufs - 1)) == 0 && kMegaRedBufs >= kMegaMaxStages + 2, "partial buffers");
 
     const uint32_t ring = smem_u32(sh.ring);
-    const int nseg = mega_segments(*gp);
-    const int gran = gp->gran;
 
-    // The tail of a tile (sum over the k-warps, rounding, store) belongs to the service warp, which runs it when every
+    // The tail of a tile (sum over the k-warps, rounding, store) belongs to the tail warp, which runs it when every
     // consumer warp has arrived on the slot's empty barrier: a consumer never blocks on a sibling. The partial sums wait
     // in one of kMegaRedBufs buffers (a warp is at most `nstage` tiles ahead of the tail).
     const __half* const xres = (kind == MOP_RESID) ? gp->out[0] : nullptr;
     if (!in_group) {
-        // a warp without a group has no part in this operator's tiles (nor in their barriers): it only keeps its ring
-        // position in step, then waits at the next operator's CTA barrier
-        int tiles = 0;
-        for (int seg = 0; seg < nseg; ++seg) tiles += mega_segment(*gp, seg, cta, ncta).nt;
-        tile_no += (uint32_t)tiles;
-        const int pos = rp.slot + tiles;
-        const int wraps = mega_div(pos, p.nstage, __frcp_rn((float)p.nstage));
-        rp.slot = pos - wraps * p.nstage;
-        rp.parity ^= (uint32_t)wraps & 1u;
+        mega_skip_tiles(rp, tile_no, my_tiles, p.nstage);
         return;
     }
-    for (int seg = 0; seg < nseg; ++seg) {
-        const MegaSeg sg = mega_segment(*gp, seg, cta, ncta);
-        int rb = sg.row0 + group;   // first row of this group in the current tile
-        // a segment's tiles come in two sizes: the first `extra` ones hold one granule more than the others
-        for (int phase = 0; phase < 2; ++phase) {
-            int ntile = phase == 0 ? sg.extra : sg.nt - sg.extra;
-            int n = (sg.base + (phase == 0 ? 1 : 0)) * gran;                          // units in a tile of this size
-            int cnt = n > group ? ((n - group + G - 1) * recipG) >> 16 : 0;          // units of this group
-            int nrows = paired ? 2 * cnt : cnt;                                      // physical rows of this group
-            // (kept opaque: under register pressure the compiler would recompute these at every use inside the tile loop)
-            asm volatile("" : "+r"(n), "+r"(cnt), "+r"(nrows), "+r"(ntile));
-            for (int ti = 0; ti < ntile; ++ti) {
-                const long long tw0 = kProf ? clock64() : 0ll;
-                mega_wait_bar(&sh.full_bar[rp.slot], rp.parity, w, 2u, k, 32u);
-                if (kProf) t_full += clock64() - tw0;
-                const int buf = (int)(tile_no & (uint32_t)(kMegaRedBufs - 1));
-                const int bufo = buf * kRedBuf;
-                // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
-                float resid = 0.f;
-                const bool res_lane = xres != nullptr && kw_id == 0 && lane < cnt;
-                if (res_lane) resid = __half2float(__ldcg(xres + rb + lane * G));
-                const uint32_t sbase = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes;
-                uint32_t bw = sbase + w_lane, bz = sbase + z_lane, bs = sbase + s_lane;
-                for (int p0 = 0; p0 < nrows; p0 += NR, bw += adv_w, bz += adv_z, bs += adv_s) {
-                    const int left = nrows - p0;
-                    uint32_t wa[NR];
-                    wa[0] = bw;
-                    if (NR > 1) wa[1 % NR] = bw + (left > 1 ? ro1 : 0u);    // rows past the end repeat row 0 (not stored)
-                    if (NR > 2) {
-                        wa[2 % NR] = bw + (left > 2 ? ro2 : 0u);
-                        wa[3 % NR] = bw + (left > 3 ? ro3 : 0u);
-                    }
-                    const long long tb0 = kProf ? clock64() : 0ll;
-                    const float v = mega_batch<INT4, NP>(xs0, tab, tab_n, u0, u1, wa, du, bz, bs, zshift, (left < NR ? left : NR) * NP, lane);
-                    if (storer && rj < left) red_w[bufo + p0] = v;
-                    if (kProf) t_batch += clock64() - tb0;
-                }
-                if (res_lane) sh.resid[(buf * kMegaMaxGroups + group) * kMegaGroupRows + lane] = resid;
-                // last read of the slot and the partials of this warp are done: one arrival tells the copy and tail warps
-                __syncwarp();
-                if (lane == 0) mbar_arrive_n(&sh.empty_bar[rp.slot], my_arrive);
-                rb += n;
-                ++tile_no;
-                mega_ring_next(rp, p.nstage);
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        const long long tw0 = kProf ? clock64() : 0ll;
+        mega_wait_bar(&sh.full_bar[rp.slot], rp.parity, w, 2u, k, 32u);
+        if (kProf) t_full += clock64() - tw0;
+        const int n = sh.tile_n[rp.slot];                                          // units in this tile
+        const int rb = sh.tile_row[rp.slot] + group;                               // first row of this group
+        const int cnt = n > group ? ((n - group + G - 1) * recipG) >> 16 : 0;      // units of this group
+        const int nrows = paired ? 2 * cnt : cnt;                                  // physical rows of this group
+        const int buf = (int)(tile_no & (uint32_t)(kMegaRedBufs - 1));
+        const int bufo = buf * kRedBuf;
+        // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
+        float resid = 0.f;
+        const bool res_lane = xres != nullptr && kw_id == 0 && lane < cnt;
+        if (res_lane) resid = __half2float(__ldcg(xres + rb + lane * G));
+        const uint32_t sbase = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes;
+        uint32_t bw = sbase + w_lane, bz = sbase + z_lane, bs = sbase + s_lane;
+        for (int p0 = 0; p0 < nrows; p0 += NR, bw += adv_w, bz += adv_z, bs += adv_s) {
+            const int left = nrows - p0;
+            uint32_t wa[NR];
+            wa[0] = bw;
+            if (NR > 1) wa[1 % NR] = bw + (left > 1 ? ro1 : 0u);    // rows past the end repeat row 0 (not stored)
+            if (NR > 2) {
+                wa[2 % NR] = bw + (left > 2 ? ro2 : 0u);
+                wa[3 % NR] = bw + (left > 3 ? ro3 : 0u);
+            }
+            const long long tb0 = kProf ? clock64() : 0ll;
+            const float v = mega_batch<INT4, NP>(xs0, tab, tab_n, u0, u1, wa, du, bz, bs, zshift, (left < NR ? left : NR) * NP, lane);
+            if (storer && rj < left) red_w[bufo + p0] = v;
+            if (kProf) t_batch += clock64() - tb0;
+        }
+        if (res_lane) sh.resid[(buf * kMegaMaxGroups + group) * kMegaGroupRows + lane] = resid;
+        // last read of the slot and the partials of this warp are done: one arrival tells the copy and tail warps
+        __syncwarp();
+        if (lane == 0) mbar_arrive_n(&sh.empty_bar[rp.slot], my_arrive);
+        ++tile_no;
+        mega_ring_next(rp, p.nstage);
+    }
+}
+
+// ---- int4 operators on the tensor cores -------------------------------------------------------------------------------
+// The arithmetic of an int4 mat-vec is bound by instruction issue, not by the multiply-adds themselves: as scalar code
+// a packed word costs 5 integer instructions to unpack and 8 multiply-adds. One warp-wide m16n8k16 step takes the
+// unpacked words of 16 rows (two registers of a row's word per step) against the matching inputs, so a word costs its
+// unpacking plus ONE further instruction. Only column 0 of the 16 x 8 result is used.
+//   lane (g, t), g = lane / 4, t = lane % 4, holds for quantisation group G the 16-byte vector 4G + t of row g of the
+//   tile's first block of 8 rows and of row g of the second block (rows 8..15; SwiGLU: the 8 up rows beside the 8
+//   gate rows). Its B fragments are the table entries of slot 4G + t (the same for every g: only the lanes with
+//   g == 0 feed column 0). After the 8 steps of a group the lanes with t == 0 hold the group's sums of rows g, g + 8.
+// Unpacking: (w & 0x000f000f) | 0x64006400 = fp16 (1024 + n0, 1024 + n4); (w & 0x00f000f0) | 0x54005400 = fp16
+// (64 + n1, 64 + n5) (the nibble sits 4 bits up in a mantissa whose unit is 1/16); the same on w >> 8. The offsets are
+// taken out by the accumulator's start value.
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// first step of an accumulator chain: no accumulator input (no registers to clear)
+__device__ __forceinline__ void mma_m16n8k16_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+template <bool TWO, bool FIRST>
+__device__ __forceinline__ void mega_mma_word(uint32_t wa, uint32_t wb, const uint4& xb, float (&acc0)[4], float (&acc1)[4])
+{
+    const uint32_t wa8 = wa >> 8;
+    const uint32_t aa = and_or(wa, 0x000f000fu, 0x64006400u), ab = and_or(wa, 0x00f000f0u, 0x54005400u);
+    const uint32_t ac = and_or(wa8, 0x000f000fu, 0x64006400u), ad = and_or(wa8, 0x00f000f0u, 0x54005400u);
+    uint32_t ba = 0, bb = 0, bc = 0, bd = 0;
+    if (TWO) {
+        const uint32_t wb8 = wb >> 8;
+        ba = and_or(wb, 0x000f000fu, 0x64006400u); bb = and_or(wb, 0x00f000f0u, 0x54005400u);
+        bc = and_or(wb8, 0x000f000fu, 0x64006400u); bd = and_or(wb8, 0x00f000f0u, 0x54005400u);
+    }
+    if (FIRST) {
+        mma_m16n8k16_first(acc0, aa, ba, ab, bb, xb.x, xb.y);   // nibbles 0, 4 | 1, 5 against (x0,x4) | (x1,x5)
+        mma_m16n8k16_first(acc1, ac, bc, ad, bd, xb.z, xb.w);   // nibbles 2, 6 | 3, 7 against (x2,x6) | (x3,x7)
+    } else {
+        mma_m16n8k16(acc0, aa, ba, ab, bb, xb.x, xb.y);
+        mma_m16n8k16(acc1, ac, bc, ad, bd, xb.z, xb.w);
+    }
+}
+
+// Consumer side of one int4 operator. Warp q works on quantisation groups [q * upw, q * upw + upw) of ALL rows of every
+// tile and leaves one partial sum per row; the tail warp adds the warps' partials in a fixed order. Rows of the slot past
+// the end of a short tile hold whatever an earlier tile left there: any bit pattern unpacks to finite numbers, and nobody
+// reads those rows' sums. The consumers do not follow the row ranges at all: the copy warp leaves a tile's first row and
+// row count beside the slot (warp 0 needs them to fetch the residual values).
+template <bool TWO, bool kProf>
+__device__ __forceinline__ void mega_consume_mma(const MegaOp* __restrict__ gp, const MegaParams& p, int k, const MegaShared& sh, MegaRing& rp,
+                                                 uint32_t& tile_no, const MegaWait& w, int my_tiles, long long& t_full, long long& t_batch)
+{
+    const int tid = (int)threadIdx.x - kMegaServiceThreads, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int kw = gp->kw, upw = gp->np, tab_n = gp->tab_n;
+    if (warp >= kw) {
+        mega_skip_tiles(rp, tile_no, my_tiles, p.nstage);
+        return;
+    }
+    const int grp0 = warp * upw;
+    int cnt = gp->ngrp - grp0;
+    cnt = cnt < upw ? cnt : upw;
+    // arrival weight on a slot's empty barrier: the working warps of the operator add up to the barrier's fixed count
+    const uint32_t my_arrive = (warp == 0) ? (kMegaBarCount - (uint32_t)kw + 1u) : 1u;
+    const bool paired = gp->paired != 0;
+    const uint32_t wrow = (uint32_t)gp->wrow, zrow = (uint32_t)gp->zrow, srow = (uint32_t)gp->srow;
+    // second block: rows 8 .. 15 of the run, or (SwiGLU) rows 0 .. 7 of the second run
+    const uint32_t blk_w = paired ? (uint32_t)gp->run_bytes : 8u * wrow;
+    const uint32_t blk_z = paired ? (uint32_t)gp->run_bytes : 8u * zrow;
+    const uint32_t blk_s = paired ? (uint32_t)gp->run_bytes : 8u * srow;
+    const uint32_t w_lane = (uint32_t)g * wrow + (uint32_t)(grp0 * 4 + t) * 16u;
+    const uint32_t z_lane = (uint32_t)gp->off_z + (uint32_t)g * zrow + (uint32_t)(grp0 >> 3) * 4u;
+    const uint32_t s_lane = (uint32_t)gp->off_s + (uint32_t)g * srow + (uint32_t)grp0 * 2u;
+    const uint32_t tab = smem_u32(sh.table);
+    const uint32_t x_lane = tab + (uint32_t)(grp0 * 4 + t) * 16u;
+    const uint32_t x_q = (uint32_t)tab_n * 16u;
+    const uint32_t c_lane = tab + (uint32_t)(4 * tab_n + grp0) * 16u;
+    constexpr int kRedBuf = kMegaConsumerWarps * kMegaRedRows;
+    float* const red_w = sh.red + warp * kMegaRedRows + g;
+    const uint32_t ring = smem_u32(sh.ring);
+    const __half* const xres = (gp->kind == MOP_RESID && warp == 0) ? gp->out[0] : nullptr;
+
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        const long long tw0 = kProf ? clock64() : 0ll;
+        mega_wait_bar(&sh.full_bar[rp.slot], rp.parity, w, 2u, k, 32u);
+        const long long tb0 = kProf ? clock64() : 0ll;
+        if (kProf) t_full += tb0 - tw0;
+        const int buf = (int)(tile_no & (uint32_t)(kMegaRedBufs - 1));
+        // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
+        float resid = 0.f;
+        bool res_lane = false;
+        if (xres != nullptr) {
+            res_lane = lane < sh.tile_n[rp.slot];
+            if (res_lane) resid = __half2float(__ldcg(xres + sh.tile_row[rp.slot] + lane));
+        }
+        const uint32_t sbase = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes;
+        float tot_a = 0.f, tot_b = 0.f;
+        uint32_t aw = sbase + w_lane, ax = x_lane, ac = c_lane;
+        int grp = grp0;
+#pragma unroll 1
+        for (int u = 0; u < cnt; ++u, aw += 64u, ax += 64u, ac += 16u, ++grp) {
+            const uint4 va = lds_v4(aw);
+            uint4 vb = make_uint4(0u, 0u, 0u, 0u);
+            if (TWO) vb = lds_v4(aw + blk_w);
+            const uint4 x0 = lds_v4(ax), x1 = lds_v4(ax + x_q), x2 = lds_v4(ax + 2u * x_q), x3 = lds_v4(ax + 3u * x_q);
+            float c0, c1;
+            asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(c0), "=f"(c1) : "r"(ac));
+            // zero words and scales of this group for the lane's rows
+            const uint32_t zo = (uint32_t)((grp >> 3) - (grp0 >> 3)) * 4u, so = (uint32_t)(grp - grp0) * 2u;
+            uint32_t zwa, zwb = 0;
+            unsigned short sca, scb = 0;
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zwa) : "r"(sbase + z_lane + zo));
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sca) : "r"(sbase + s_lane + so));
+            if (TWO) {
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zwb) : "r"(sbase + z_lane + blk_z + zo));
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(scb) : "r"(sbase + s_lane + blk_s + so));
+            }
+            float acc0[4] = {c0, 0.f, c0, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+            mega_mma_word<TWO, false>(va.x, vb.x, x0, acc0, acc1);
+            mega_mma_word<TWO, false>(va.y, vb.y, x1, acc0, acc1);
+            mega_mma_word<TWO, false>(va.z, vb.z, x2, acc0, acc1);
+            mega_mma_word<TWO, false>(va.w, vb.w, x3, acc0, acc1);
+            const int zs = (grp & 7) * 4;
+            const float za = (float)((zwa >> zs) & 0xFu);
+            tot_a = fmaf(half_bits_to_float(sca), fmaf(-za, c1, acc0[0] + acc1[0]), tot_a);
+            if (TWO) {
+                const float zb = (float)((zwb >> zs) & 0xFu);
+                tot_b = fmaf(half_bits_to_float(scb), fmaf(-zb, c1, acc0[2] + acc1[2]), tot_b);
             }
         }
+        if (t == 0) {
+            red_w[buf * kRedBuf] = tot_a;
+            if (TWO) red_w[buf * kRedBuf + 8] = tot_b;
+        }
+        if (res_lane) sh.resid[buf * (kMegaMaxGroups * kMegaGroupRows) + lane] = resid;
+        if (kProf) t_batch += clock64() - tb0;
+        // last read of the slot and the partials of this warp are done: one arrival tells the copy and tail warps
+        __syncwarp();
+        if (lane == 0) mbar_arrive_n(&sh.empty_bar[rp.slot], my_arrive);
+        ++tile_no;
+        mega_ring_next(rp, p.nstage);
     }
 }
 
-// ---- service warp: the stream of this CTA's tiles over the whole token ------------------------------------------------
-// A cursor walks this CTA's tiles in order (operator by operator, segment by segment). Everything that changes only
-// with the operator or the segment is kept in registers; a step inside a segment costs a handful of instructions.
-struct MegaCursor {
-    int k;             // operator (nops: past the end)
-    int seg, nseg;     // segment of the operator
-    int ti, nt;        // tile of the segment, tiles in the segment
-    int n_lo, extra;   // units per tile: n_lo (+ gran for the first `extra` tiles)
-    int gran;
-    int row, n;        // first unit and units of the current tile
-    int left;          // tiles of operator k that follow the current one on this CTA
-    bool fresh;        // the cursor has just entered an operator or a segment (per-operator state must be reloaded)
+// ---- the hot loop of the int4 operators, compiled as a function of its own --------------------------------------------
+// Inlined into the kernel, the tile loop shares the register file of a 736-thread CTA (80 registers a thread) with
+// everything else the kernel keeps alive, and spills. As a separate function it gets the whole budget: the caller's
+// state is saved once per operator. Everything it touches is addressed by 32-bit shared-memory addresses.
+struct MegaWaitShared {      // in shared memory: what a wait needs when it does not succeed at once
+    long long budget;        // SM cycles
+    DeviceStatus* status;
+    unsigned int abort;      // some role of this CTA gave up
+    unsigned int pad;
+};
+struct MegaLoop {
+    uint32_t ring, full_bar, empty_bar, red, resid, tile_row, tile_n, table, wait;   // shared-memory addresses
+    int nstage, slot_bytes, k, my_tiles;
+};
+struct MegaLoopState {
+    int slot;
+    uint32_t parity, tile_no;
 };
 
-__device__ __forceinline__ int mega_my_tiles(const MegaOp& op, int cta, int ncta)
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity)
 {
-    int t = 0;
-    const int nseg = mega_segments(op);
-    for (int s = 0; s < nseg; ++s) t += mega_segment(op, s, cta, ncta).nt;
-    return t;
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_suspend_a(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ unsigned short lds_u16(uint32_t a)
+{
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+
+// the barrier was not complete at the first look: sleep between polls, watch the abort flag and the clock
+__device__ __noinline__ void mega_wait_slow(uint32_t bar, uint32_t parity, uint32_t ws, unsigned int code, int detail)
+{
+    const long long t0 = clock64();
+    long long budget;
+    asm volatile("ld.shared.s64 %0, [%1];" : "=l"(budget) : "r"(ws));
+    for (uint32_t i = 0; i < (1u << 30); ++i) {
+        if (mbar_try_wait_suspend_a(bar, parity, 1000u)) return;
+        __nanosleep(32u);
+        if (lds_u32(ws + 16u)) return;
+        if (clock64() - t0 > budget) break;
+    }
+    DeviceStatus* status;
+    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(status) : "r"(ws + 8u));
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(ws + 16u), "r"(1u) : "memory");
+    if (atomicCAS(&status->error, 0u, code) == 0u) status->detail = (unsigned int)detail;
 }
 
-__device__ __forceinline__ void mega_cursor_segment(const MegaOp& op, int cta, int ncta, MegaCursor& c)
+// the arithmetic of one tile for one warp: two quantisation groups of the tile's one or two blocks of 8 rows
+template <bool TWO>
+__device__ __forceinline__ void mega_tile_math(uint32_t sbase, uint32_t a_w, uint32_t blk_w, uint32_t o1, uint32_t a_z, uint32_t a_zb, uint32_t a_s,
+                                           uint32_t a_sb, uint32_t so1, int zs0, const uint4 (&xr0)[4], const uint4 (&xr1)[4], float c00, float c01,
+                                           float c10, float c11, uint32_t red_a, int lane)
 {
-    // first segment >= c.seg with tiles (the caller knows there is one)
-    for (; c.seg < c.nseg; ++c.seg) {
-        const MegaSeg sg = mega_segment(op, c.seg, cta, ncta);
-        if (sg.nt > 0) {
-            c.ti = 0; c.nt = sg.nt; c.n_lo = sg.base * c.gran; c.extra = sg.extra; c.row = sg.row0;
-            c.n = c.n_lo + (sg.extra > 0 ? c.gran : 0);
-            return;
+    float tot_a, tot_b = 0.f;
+    {
+        // first group
+        const uint4 va = lds_v4(sbase + a_w);
+        uint4 vb = make_uint4(0u, 0u, 0u, 0u);
+        if (TWO) vb = lds_v4(sbase + a_w + blk_w);
+        float acc0[4], acc1[4];
+        mega_mma_word<TWO, true>(va.x, vb.x, xr0[0], acc0, acc1);
+        mega_mma_word<TWO, false>(va.y, vb.y, xr0[1], acc0, acc1);
+        mega_mma_word<TWO, false>(va.z, vb.z, xr0[2], acc0, acc1);
+        mega_mma_word<TWO, false>(va.w, vb.w, xr0[3], acc0, acc1);
+        tot_a = acc0[0] + acc1[0] + c00;
+        if (TWO) tot_b = acc0[2] + acc1[2] + c00;
+    }
+    float sec_a, sec_b = 0.f;
+    {
+        // second group
+        const uint4 va = lds_v4(sbase + a_w + o1);
+        uint4 vb = make_uint4(0u, 0u, 0u, 0u);
+        if (TWO) vb = lds_v4(sbase + a_w + blk_w + o1);
+        float acc0[4], acc1[4];
+        mega_mma_word<TWO, true>(va.x, vb.x, xr1[0], acc0, acc1);
+        mega_mma_word<TWO, false>(va.y, vb.y, xr1[1], acc0, acc1);
+        mega_mma_word<TWO, false>(va.z, vb.z, xr1[2], acc0, acc1);
+        mega_mma_word<TWO, false>(va.w, vb.w, xr1[3], acc0, acc1);
+        sec_a = acc0[0] + acc1[0] + c10;
+        if (TWO) sec_b = acc0[2] + acc1[2] + c10;
+    }
+    {
+        const uint32_t zw = lds_u32(sbase + a_z);
+        const unsigned short s0 = lds_u16(sbase + a_s), s1 = lds_u16(sbase + a_s + so1);
+        const float z0 = (float)((zw >> zs0) & 0xFu), z1 = (float)((zw >> (zs0 + 4)) & 0xFu);
+        tot_a = half_bits_to_float(s0) * fmaf(-z0, c01, tot_a);
+        tot_a = fmaf(half_bits_to_float(s1), fmaf(-z1, c11, sec_a), tot_a);
+        if ((lane & 3) == 0) sts_f32(red_a, tot_a);
+    }
+    if (TWO) {
+        const uint32_t zw = lds_u32(sbase + a_zb);
+        const unsigned short s0 = lds_u16(sbase + a_sb), s1 = lds_u16(sbase + a_sb + so1);
+        const float z0 = (float)((zw >> zs0) & 0xFu), z1 = (float)((zw >> (zs0 + 4)) & 0xFu);
+        tot_b = half_bits_to_float(s0) * fmaf(-z0, c01, tot_b);
+        tot_b = fmaf(half_bits_to_float(s1), fmaf(-z1, c11, sec_b), tot_b);
+        if ((lane & 3) == 0) sts_f32(red_a + 32u, tot_b);
+    }
+}
+
+// Exactly two quantisation groups per warp (an odd last one: zero inputs against the first group's weights): the warp's
+// B fragments and group constants stay in registers for the whole operator, and a tile is straight-line code.
+template <bool TWO, bool kProf>
+__device__ __noinline__ MegaLoopState mega_consume_mma_reg(const MegaOp* __restrict__ gp, const MegaLoop a, MegaLoopState st, long long* prof)
+{
+    const int lane = threadIdx.x & 31, warp = ((int)threadIdx.x - kMegaServiceThreads) >> 5;
+    const int kw = gp->kw;
+    if (warp >= kw) {
+        MegaRing rp{st.slot, st.parity};
+        mega_skip_tiles(rp, st.tile_no, a.my_tiles, a.nstage);
+        st.slot = rp.slot;
+        st.parity = rp.parity;
+        return st;
+    }
+    const uint32_t my_arrive = (warp == 0) ? (kMegaBarCount - (uint32_t)kw + 1u) : 1u;
+    uint32_t blk_w, a_w, a_z, a_zb, a_s, a_sb, o1;
+    int zs0;
+    uint4 xr0[4], xr1[4];   // stationary inputs
+    float c00, c01, c10 = 0.f, c11 = 0.f;
+    {
+        const int g = lane >> 2, t = lane & 3, grp0 = warp * 2, tab_n = gp->tab_n;
+        const bool second = grp0 + 1 < gp->ngrp;
+        const bool paired = gp->paired != 0;
+        const uint32_t wrow = (uint32_t)gp->wrow, zrow = (uint32_t)gp->zrow, srow = (uint32_t)gp->srow;
+        // second block: rows 8 .. 15 of the run, or (SwiGLU) rows 0 .. 7 of the second run
+        blk_w = paired ? (uint32_t)gp->run_bytes : 8u * wrow;
+        a_w = (uint32_t)g * wrow + (uint32_t)(grp0 * 4 + t) * 16u;
+        o1 = second ? 64u : 0u;
+        a_z = (uint32_t)gp->off_z + (uint32_t)g * zrow + (uint32_t)(grp0 >> 3) * 4u;   // both groups sit in one zero word
+        a_zb = a_z + (paired ? (uint32_t)gp->run_bytes : 8u * zrow);
+        a_s = (uint32_t)gp->off_s + (uint32_t)g * srow + (uint32_t)grp0 * 2u;
+        a_sb = a_s + (paired ? (uint32_t)gp->run_bytes : 8u * srow);
+        zs0 = (grp0 & 7) * 4;
+        const uint32_t ax = a.table + (uint32_t)(grp0 * 4 + t) * 16u, xq = (uint32_t)tab_n * 16u, ac = a.table + (uint32_t)(4 * tab_n + grp0) * 16u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            xr0[q] = lds_v4(ax + (uint32_t)q * xq);
+            xr1[q] = second ? lds_v4(ax + (uint32_t)q * xq + 64u) : make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(c00), "=f"(c01) : "r"(ac));
+        if (second) asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(c10), "=f"(c11) : "r"(ac + 16u));
     }
-}
+    const uint32_t so1 = o1 >> 5;   // 2 bytes on to the second group's scale, 0 without one
+    const uint32_t red_w = a.red + (uint32_t)(warp * kMegaRedRows + (lane >> 2)) * 4u;
+    constexpr uint32_t kRedBufBytes = kMegaConsumerWarps * kMegaRedRows * 4;
+    const __half* const xres = (gp->kind == MOP_RESID && warp == 0) ? gp->out[0] : nullptr;
+    int slot = st.slot;
+    uint32_t parity = st.parity, tile_no = st.tile_no;
+    long long t_full = 0, t_batch = 0;
 
-// positions `c` on the first tile of the first operator >= c.k that has tiles on this CTA
-__device__ __forceinline__ void mega_cursor_seek(const MegaParams& p, int cta, int ncta, MegaCursor& c)
-{
-    for (; c.k < p.nops; ++c.k) {
-        const MegaOp& op = p.ops[c.k];
-        if (!op.has_tiles) continue;
-        const int total = mega_my_tiles(op, cta, ncta);
-        if (total == 0) continue;
-        c.nseg = mega_segments(op);
-        c.gran = op.gran;
-        c.seg = 0;
-        mega_cursor_segment(op, cta, ncta, c);
-        c.left = total - 1;
-        c.fresh = true;
-        return;
+    for (int ti = 0; ti < a.my_tiles; ++ti) {
+        const long long tw0 = kProf ? clock64() : 0ll;
+        const uint32_t fb = a.full_bar + (uint32_t)slot * 8u;
+        if (!mbar_try_wait_a(fb, parity)) mega_wait_slow(fb, parity, a.wait, 2u, a.k);
+        const long long tb0 = kProf ? clock64() : 0ll;
+        if (kProf) t_full += tb0 - tw0;
+        const uint32_t bufo = (tile_no & (uint32_t)(kMegaRedBufs - 1)) * kRedBufBytes;
+        // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
+        if (xres != nullptr) {
+            const int n = (int)lds_u32(a.tile_n + (uint32_t)slot * 4u);
+            if (lane < n) {
+                const int row = (int)lds_u32(a.tile_row + (uint32_t)slot * 4u);
+                sts_f32(a.resid + ((tile_no & (uint32_t)(kMegaRedBufs - 1)) * (uint32_t)(kMegaMaxGroups * kMegaGroupRows) + (uint32_t)lane) * 4u,
+                        __half2float(__ldcg(xres + row + lane)));
+            }
+        }
+        const uint32_t sbase = a.ring + (uint32_t)slot * (uint32_t)a.slot_bytes;
+#ifndef ML2_DIAG_NOMATH
+        mega_tile_math<TWO>(sbase, a_w, blk_w, o1, a_z, a_zb, a_s, a_sb, so1, zs0, xr0, xr1, c00, c01, c10, c11, red_w + bufo, lane);
+#endif
+        if (kProf) t_batch += clock64() - tb0;
+        // last read of the slot and the partials of this warp are done: one arrival tells the copy and tail warps
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(a.empty_bar + (uint32_t)slot * 8u), "r"(my_arrive) : "memory");
+        ++tile_no;
+        if (++slot == a.nstage) { slot = 0; parity ^= 1u; }
     }
-}
-
-__device__ __forceinline__ void mega_cursor_next(const MegaParams& p, int cta, int ncta, MegaCursor& c)
-{
-    if (c.left != 0 && c.ti + 1 < c.nt) {   // the common step: next tile of the same segment
-        --c.left;
-        ++c.ti;
-        c.row += c.n;
-        c.n = c.n_lo + (c.ti < c.extra ? c.gran : 0);
-        return;
-    }
-    if (c.left == 0) {
-        ++c.k;
-        mega_cursor_seek(p, cta, ncta, c);
-        return;
-    }
-    --c.left;
-    ++c.seg;
-    mega_cursor_segment(p.ops[c.k], cta, ncta, c);
-    c.fresh = true;   // the segment changed: matrix and output pointers change with it
-}
-
-// this CTA's share of operator k is stored: publish it (the warp barrier orders every lane's stores before the release)
-__device__ __forceinline__ void mega_publish(const MegaParams& p, int k, int lane)
-{
-    const MegaOp& op = p.ops[k];
-    __syncwarp();
-    if ((op.kind == MOP_PARTIAL || op.kind == MOP_CLS) && op.tp > 1) {
-        if (lane < op.tp) red_release_sys_add(op.peer_done[lane], 1u);   // on every rank's counter, after the peer stores
-    } else if (lane == 0) {
-        red_release_gpu_add(&p.done[k], 1u);
-    }
+    if (kProf) { prof[0] += t_full; prof[1] += t_batch; }
+    st.slot = slot;
+    st.parity = parity;
+    st.tile_no = tile_no;
+    return st;
 }
 
 // kProf adds cycle counters around the waits (diagnostics); the production instantiation carries none.
@@ -658,14 +903,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     extern __shared__ __align__(128) unsigned char smem_raw[];   // [ring: nstage * slot_bytes][input table | attention scores, partial outputs]
     __shared__ __align__(8) uint64_t full_bar[kMegaMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMegaMaxStages];
-    __shared__ float s_red[kMegaRedBufs * kMegaConsumerWarps * kMegaGroupRows];
+    __shared__ float s_red[kMegaRedBufs * kMegaConsumerWarps * kMegaRedRows];
     __shared__ float s_part[2][kMegaConsumerWarps];
     __shared__ float s_resid[kMegaRedBufs * kMegaMaxGroups * kMegaGroupRows];
     __shared__ float s_att_tmp[kMegaConsumerWarps];
     __shared__ __align__(16) __half s_q[kHeadMax];
     __shared__ float s_best_v[kMegaConsumerWarps];
     __shared__ int s_best_i[kMegaConsumerWarps];
-    __shared__ unsigned int s_abort;
+    __shared__ int s_tile_row[kMegaMaxStages], s_tile_n[kMegaMaxStages];
+    __shared__ __align__(16) uint4 s_meta[kMegaRedBufs][2];   // the last 32 bytes of the descriptors of the tiles in flight (copy warp -> tail warp)
+    __shared__ __align__(16) MegaWaitShared s_wait;
+    volatile unsigned int& s_abort = s_wait.abort;
     __shared__ unsigned int s_tailed;   // tiles whose tail has run (tail warp -> copy warp)
     __shared__ unsigned int s_released; // tiles known to be consumed (copy warp -> tail warp)
     // the consumers' view of the current operator and of the next one (fetched one operator ahead, so that no field of an
@@ -686,7 +934,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kMegaBarCount);
         }
-        s_abort = 0;
+        s_wait.abort = 0;
+        s_wait.budget = p.wait_cycles;
+        s_wait.status = p.status;
         s_tailed = 0;
         s_released = 0;
         mbar_fence_init();
@@ -695,76 +945,68 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     __syncthreads();
 
     MegaWait w;
-    w.abort_flag = &s_abort;
+    w.abort_flag = &s_wait.abort;
     w.status = p.status;
     w.budget = p.wait_cycles;
 
-    if (warp == kMegaConsumerWarps) {
+    if (warp == 0) {
         // ================= copy warp ==========================================================================
         // Tile t of this CTA (counted over the whole token) lives in ring slot t % nstage. When all consumer warps have
         // arrived on a slot's empty barrier, the slot is refilled with the tile that is `nstage` further on. Weights
         // do not depend on activations, so the copies run ahead of the arithmetic across operator boundaries.
+        // Lanes 0 .. 5 own one copy of a tile each (their 16 bytes of the descriptor), lane 6 the tile's row, size and
+        // byte count; the next tile's descriptor is fetched while this one waits for its slot.
         const uint64_t pol = policy_evict_first();
+        const int t_begin = p.tile_begin[cta], ntile = p.tile_begin[cta + 1] - t_begin;
+        const uint4* td = reinterpret_cast<const uint4*>(p.tiles + t_begin) + (lane < 8 ? lane : 7);
+        constexpr size_t kStride = sizeof(MegaTile) / sizeof(uint4);
+        auto fetch = [&](int i) -> uint4 {   // issued where it stands (not moved by the compiler): two tiles before it is needed
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (i < ntile)
+                asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(td + (size_t)i * kStride));
+            return v;
+        };
         MegaRing ri{0, 0u};
-        MegaCursor ci;
-        ci.k = 0;
-        mega_cursor_seek(p, cta, ncta, ci);
-        uint32_t issued = 0;
         long long tp_wait = 0, tp_all0 = now();
-        // this lane's copy: part (lane % 3) of run (lane / 3): weights, zero words, scales
-        const int my_run = lane / 3, my_part = lane - my_run * 3;
-        bool i_issuer = false;
-        uint32_t i_rowbytes = 0, i_off = 0, i_allbytes = 0;
-        const unsigned char* i_src = nullptr;
-        while (ci.k < p.nops) {
-            if (issued >= (uint32_t)p.nstage) {
+        uint4 nxt = fetch(0), nxt2 = fetch(1);
+        for (int i = 0; i < ntile; ++i) {
+            const uint4 cur = nxt;
+            nxt = nxt2;
+            nxt2 = fetch(i + 2);
+            if (i >= p.nstage) {
                 const long long tw0 = now();
                 if (lane == 0) {
-                    mega_wait_bar(&empty_bar[ri.slot], ri.parity ^ 1u, w, 1u, ci.k, 256u);
-                    // tile (issued - nstage) is consumed. The tail warp learns that from the barrier's phase parity, which
+                    mega_wait_bar(&empty_bar[ri.slot], ri.parity ^ 1u, w, 1u, i, 256u);
+                    // tile (i - nstage) is consumed. The tail warp learns that from the barrier's phase parity, which
                     // repeats after two refills: this counter settles it if the tail warp ever falls that far behind
-                    *(volatile unsigned int*)&s_released = issued - (uint32_t)p.nstage + 1u;
+                    *(volatile unsigned int*)&s_released = (unsigned int)(i - p.nstage) + 1u;
                     // the tail warp reads the partial sums of a tile from one of kMegaRedBufs buffers and tells tiles
                     // apart by the barrier's phase parity: it must not fall further behind than that allows
                     const long long t0 = clock64();
-                    while ((int)(issued - *(volatile unsigned int*)&s_tailed) > kMegaRedBufs - 1 && !s_abort) {
-                        if (clock64() - t0 > w.budget) { mega_give_up(w, 7u, ci.k); break; }
+                    while ((int)((unsigned int)i - *(volatile unsigned int*)&s_tailed) > kMegaRedBufs - 1 && !s_abort) {
+                        if (clock64() - t0 > w.budget) { mega_give_up(w, 7u, i); break; }
                     }
                 }
                 __syncwarp();
                 tp_wait += now() - tw0;
+                if (s_abort) break;   // some wait ran out: no further copies
             }
-            if (ci.fresh) {
-                const MegaOp* __restrict__ gp = p.ops + ci.k;
-                const int nruns = gp->paired ? 2 : 1;
-                const uint32_t wrow = (uint32_t)gp->wrow, zrow = (uint32_t)gp->zrow, srow = (uint32_t)gp->srow;
-                i_issuer = lane < 3 * nruns && (gp->fmt == 0 || my_part == 0);
-                i_allbytes = (uint32_t)nruns * (wrow + zrow + srow);
-                i_rowbytes = my_part == 0 ? wrow : (my_part == 1 ? zrow : srow);
-                i_off = (uint32_t)my_run * (uint32_t)gp->run_bytes + (my_part == 0 ? 0u : (my_part == 1 ? (uint32_t)gp->off_z : (uint32_t)gp->off_s));
-                if (i_issuer) {
-                    const QWPtrs q = gp->mat[gp->paired ? my_run : ci.seg];
-                    i_src = my_part == 0 ? reinterpret_cast<const unsigned char*>(q.w)
-                                         : (my_part == 1 ? reinterpret_cast<const unsigned char*>(q.z) : reinterpret_cast<const unsigned char*>(q.s));
-                    i_src += (size_t)ci.row * i_rowbytes;
-                }
-                ci.fresh = false;
-            }
-            const uint32_t n = (uint32_t)ci.n;
+            const uint32_t total = __shfl_sync(0xffffffffu, cur.w, 6);
+            // the tile's row and size for the consumers, its whole tail part for the tail warp: ordered before their reads by the barriers
+            if (lane == 6) { s_tile_row[ri.slot] = (int)cur.x; s_tile_n[ri.slot] = (int)cur.y; }
+            if (lane == 6 || lane == 7) s_meta[i & (kMegaRedBufs - 1)][lane - 6] = cur;
+            __syncwarp();
 #ifdef ML2_DIAG_NOCOPY
             if (lane == 0) mbar_arrive(&full_bar[ri.slot]);   // pipeline probe: no weight copies
-            i_issuer = false;
 #else
-            if (lane == 0) mbar_arrive_expect_tx(&full_bar[ri.slot], n * i_allbytes);
-#endif
+            if (lane == 0) mbar_arrive_expect_tx(&full_bar[ri.slot], total);
             __syncwarp();
-            if (i_issuer) {
-                bulk_g2s(smem_raw + (size_t)ri.slot * p.slot_bytes + i_off, i_src, n * i_rowbytes, &full_bar[ri.slot], pol);
-                i_src += (size_t)n * i_rowbytes;
+            if (lane < 6 && cur.z != 0u) {
+                const void* src = reinterpret_cast<const void*>((uint64_t)cur.x | ((uint64_t)cur.y << 32));
+                bulk_g2s(smem_raw + (size_t)ri.slot * p.slot_bytes + cur.w, src, cur.z, &full_bar[ri.slot], pol);
             }
-            mega_cursor_next(p, cta, ncta, ci);
+#endif
             mega_ring_next(ri, p.nstage);
-            ++issued;
         }
         if (kProf && p.prof && lane == 0) {
             long long* o = p.prof + (size_t)cta * 64;
@@ -774,71 +1016,116 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         return;
     }
 
-    if (warp == kMegaConsumerWarps + 1) {
+    if (warp == 1) {
         // ================= tail warp ===========================================================================
         // When all consumer warps have arrived on a slot's empty barrier, the tile that was in it gets its tail: the
-        // fixed-order sum over the k-warps of every row's group, the operator's rounding and store. After the tail of
+        // fixed-order sum over the warps' partials of every row, the operator's rounding and store. After the tail of
         // the operator's last tile on this CTA the operator is published (release) on its device-wide counter.
+        const int ntile = p.tile_begin[cta + 1] - p.tile_begin[cta];
         MegaRing rf{0, 0u};
-        MegaCursor cf;
-        cf.k = 0;
-        mega_cursor_seek(p, cta, ncta, cf);
-        uint32_t tailed = 0;
-        long long tf_wait = 0, tf_all0 = now();
-        int f_kind = 0, f_G = 1, f_kw = 1, f_recipG = 65536;
-        bool f_paired = false;
-        __half* f_out = nullptr;
-        const MegaOp* f_gp = p.ops;
-        while (cf.k < p.nops) {
-            if (cf.fresh) {
-                f_gp = p.ops + cf.k;
-                f_kind = f_gp->kind; f_G = f_gp->groups; f_kw = f_gp->kw; f_paired = f_gp->paired != 0;
-                f_recipG = (65536 + f_G - 1) / f_G;
-                f_out = f_gp->out[f_kind == MOP_QKV ? cf.seg : 0];
-                if (f_kind == MOP_QKV && cf.seg > 0) f_out += (long long)p.pos * p.kv_row_stride;
-                cf.fresh = false;
-            }
+        long long tf_wait = 0, tf_all0 = now(), tf_sum = 0, tf_next = 0, tf_pub = 0, tf_epi = 0;
+        for (int i = 0; i < ntile; ++i) {
             const long long tw0 = now();
             if (lane == 0 && !mbar_try_wait(&empty_bar[rf.slot], rf.parity)) {
                 const long long t0 = clock64();
-                for (uint32_t i = 0; i < (1u << 30); ++i) {
+                for (uint32_t it = 0; it < (1u << 30); ++it) {
                     if (mbar_try_wait_suspend(&empty_bar[rf.slot], rf.parity, 1000u)) break;
                     __nanosleep(128u);
-                    if ((int)(*(volatile unsigned int*)&s_released - tailed) > 0 || s_abort) break;
-                    if (clock64() - t0 > w.budget) { mega_give_up(w, 3u, cf.k); break; }
+                    if ((int)(*(volatile unsigned int*)&s_released - (unsigned int)i) > 0 || s_abort) break;
+                    if (clock64() - t0 > w.budget) { mega_give_up(w, 3u, i); break; }
                 }
             }
             __syncwarp();
-            tf_wait += now() - tw0;
-            const int buf = (int)(tailed & (uint32_t)(kMegaRedBufs - 1));
-            const float* red = s_red + buf * (kMegaConsumerWarps * kMegaGroupRows);
-            for (int j = lane; j < cf.n; j += 32) {
-                const int i = (j * f_recipG) >> 16, g = j - i * f_G;   // unit j is unit i of group g
-                const float* rg = red + g * f_kw * kMegaGroupRows + (f_paired ? 2 * i : i);
+            const long long ts0 = now();
+            tf_wait += ts0 - tw0;
+            const int buf = i & (kMegaRedBufs - 1);
+            // what the copy warp left about this tile (the last 32 bytes of its descriptor)
+            const uint4 m0 = s_meta[buf][0], m1 = s_meta[buf][1];
+            const int row = (int)m0.x, n = (int)m0.y;
+            const int k = (int)(m0.z & 0xffffu);
+            const int f_kind = (int)(m1.z & 7u), f_kw = (int)((m1.z >> 8) & 0xffu), f_G = (int)((m1.z >> 16) & 0xffu);
+            const bool f_paired = (m1.z & 8u) != 0, f_mma = (m1.z & 16u) != 0;
+            __half* f_out = reinterpret_cast<__half*>((uint64_t)m1.x | ((uint64_t)m1.y << 32));
+            if (m0.z & kTileCacheRow) f_out += (long long)p.pos * p.kv_row_stride;
+            const MegaOp* f_gp = p.ops + k;
+            const float* red = s_red + buf * (kMegaConsumerWarps * kMegaRedRows);
+#ifdef ML2_DIAG_NOTAIL
+            if (false) {
+#else
+            if (f_mma) {
+#endif
+                // int4: every working warp left one partial per row (second block / up rows 8 further on). Two lanes per
+                // unit add half of the warps each, in a fixed order; all loads are issued before the first addition.
+                constexpr int kHalf = (kMegaConsumerWarps + 1) / 2;
+                const int j = lane & 15, kh = (f_kw + 1) >> 1;
+                const int q0 = lane < 16 ? 0 : kh, nq = lane < 16 ? kh : f_kw - kh;
+                const float* rq = red + q0 * kMegaRedRows + j;
+                float va[kHalf], vb[kHalf];
+#pragma unroll
+                for (int q = 0; q < kHalf; ++q) {
+                    va[q] = q < nq ? rq[q * kMegaRedRows] : 0.f;
+                    vb[q] = (f_paired && q < nq) ? rq[q * kMegaRedRows + 8] : 0.f;
+                }
                 float sa = 0.f, sb = 0.f;
-                for (int q = 0; q < f_kw; ++q) {
-                    sa += rg[q * kMegaGroupRows];
-                    if (f_paired) sb += rg[q * kMegaGroupRows + 1];
+#pragma unroll
+                for (int q = 0; q < kHalf; ++q) { sa += va[q]; sb += vb[q]; }
+                sa += __shfl_xor_sync(0xffffffffu, sa, 16);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 16);
+                const long long te0 = now();
+                tf_epi -= te0 - ts0;
+                if (lane < n) {
+                    const float resid = (f_kind == MOP_RESID) ? s_resid[buf * (kMegaMaxGroups * kMegaGroupRows) + lane] : 0.f;
+                    mega_epilogue(f_gp, f_kind, f_out, row + lane, sa, sb, resid);
                 }
-                const float resid = (f_kind == MOP_RESID) ? s_resid[(buf * kMegaMaxGroups + g) * kMegaGroupRows + i] : 0.f;
-                mega_epilogue(f_gp, f_kind, f_out, cf.row + j, sa, sb, resid);
+#ifdef ML2_DIAG_NOTAIL
+            } else if (false) {
+#else
+            } else {
+#endif
+                const int f_recipG = (65536 + f_G - 1) / f_G;
+                for (int j = lane; j < n; j += 32) {
+                    const int u = (j * f_recipG) >> 16, g = j - u * f_G;   // unit j is unit u of group g
+                    const float* rg = red + g * f_kw * kMegaRedRows + (f_paired ? 2 * u : u);
+                    float sa = 0.f, sb = 0.f;
+                    for (int q = 0; q < f_kw; ++q) {
+                        sa += rg[q * kMegaRedRows];
+                        if (f_paired) sb += rg[q * kMegaRedRows + 1];
+                    }
+                    const float resid = (f_kind == MOP_RESID) ? s_resid[(buf * kMegaMaxGroups + g) * kMegaGroupRows + u] : 0.f;
+                    mega_epilogue(f_gp, f_kind, f_out, row + j, sa, sb, resid);
+                }
             }
-            if (cf.left == 0) mega_publish(p, cf.k, lane);
-            ++tailed;
+            const long long ts1 = now();
+            tf_sum += ts1 - ts0;
+            tf_epi += ts1 - ts0;
+            // this CTA's share of the operator is stored: publish it (the warp barrier orders every lane's stores before the release)
             __syncwarp();
-            if (lane == 0) *(volatile unsigned int*)&s_tailed = tailed;   // the partial buffer is free again
-            mega_cursor_next(p, cta, ncta, cf);
+            const long long tpb0 = now();
+            if (m0.z & kTileLast) {
+                if (m1.z & 32u) {
+                    if (lane < f_gp->tp) red_release_sys_add(f_gp->peer_done[lane], 1u);   // on every rank's counter, after the peer stores
+                } else if (lane == 0) {
+                    red_release_gpu_add(&p.done[k], 1u);
+                }
+            }
+            tf_pub += now() - tpb0;
+            if (lane == 0) *(volatile unsigned int*)&s_tailed = (unsigned int)i + 1u;   // the partial buffer is free again
             mega_ring_next(rf, p.nstage);
+            tf_next += now() - ts1;
         }
         if (kProf && p.prof && lane == 0) {
             long long* o = p.prof + (size_t)cta * 64;
             o[34] = now() - tf_all0;
             o[35] = tf_wait;
+            o[36] = tf_epi; o[37] = tf_sum; o[38] = tf_next; o[39] = tf_pub;
         }
         return;
     }
 
-    // ================= consumers =========================================================================
+    // ================= consumers (numbered from 0 after the two service warps) ================================
+    {
+    const int tid = (int)threadIdx.x - kMegaServiceThreads;
+    const int warp = tid >> 5;
     MegaShared sh;
     sh.ring = smem_raw;
     sh.table = smem_raw + (size_t)p.nstage * p.slot_bytes;
@@ -847,13 +1134,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     sh.red = s_red;
     sh.part = &s_part[0][0];
     sh.resid = s_resid;
+    sh.tile_row = s_tile_row;
+    sh.tile_n = s_tile_n;
     MegaRing rp{0, 0u};
     uint32_t tile_no = 0;
+    int next_tiles = p.op_tiles[cta];   // this CTA's tiles of operator 0; the next operator's count is fetched one operator ahead
     long long t_dep = 0, t_full = 0, t_attn = 0, t_pro = 0, t_batch = 0, t_all0 = now();
-    long long tk_dep[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tk_pro[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tk_run[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long tk_dep[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tk_pro[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tk_run[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tk_batch[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tk_full[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int k = 0; k < p.nops; ++k) {
         const MegaOp* gp = &s_ops[k & 1];
         const MegaOp& op = *gp;
+        const int my_tiles = next_tiles;
+        if (k + 1 < p.nops) next_tiles = __ldg(p.op_tiles + (size_t)(k + 1) * ncta + cta);
         const int kk = (op.kind == MOP_RESID && op.rows > p.dim) ? 7 : op.kind;
 
         // RMSNorm weights do not depend on the previous operator: fetch them before the wait
@@ -1063,9 +1355,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         }
 
         // ---- weight operators: prepared input table, once per CTA ----------------------------------------------------
-        const int my_tiles = mega_my_tiles(op, cta, ncta);
         const bool is_int4 = op.fmt == 0;
-        const int tab_n = op.kw * 32 * op.np;
+        const int tab_n = op.tab_n;
         uint4* tab = reinterpret_cast<uint4*>(sh.table);
         const int nthr = is_int4 ? tab_n * 4 : tab_n;   // table builders: one per 8 inputs, whole warps
         if (op.pro == 0) {
@@ -1178,17 +1469,32 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         t_pro += now() - tq0;
         tk_pro[kk] += now() - tq0;
 
-        const long long trun0 = now();
+        const long long trun0 = now(), tb_before = t_batch, tf_before = t_full;
         if (is_int4) {
-            if (op.np == 1) mega_consume<true, 1, kProf>(gp, p, k, sh, rp, tile_no, w, t_full, t_batch);
-            else mega_consume<true, 2, kProf>(gp, p, k, sh, rp, tile_no, w, t_full, t_batch);
+            if (op.np <= 2) {
+                MegaLoop la;
+                la.ring = smem_u32(sh.ring); la.full_bar = smem_u32(full_bar); la.empty_bar = smem_u32(empty_bar);
+                la.red = smem_u32(s_red); la.resid = smem_u32(s_resid); la.tile_row = smem_u32(s_tile_row); la.tile_n = smem_u32(s_tile_n);
+                la.table = smem_u32(sh.table); la.wait = smem_u32(&s_wait);
+                la.nstage = p.nstage; la.slot_bytes = p.slot_bytes; la.k = k; la.my_tiles = my_tiles;
+                MegaLoopState ls{rp.slot, rp.parity, tile_no};
+                long long pr[2] = {0, 0};
+                ls = op.two ? mega_consume_mma_reg<true, kProf>(gp, la, ls, pr) : mega_consume_mma_reg<false, kProf>(gp, la, ls, pr);
+                rp.slot = ls.slot; rp.parity = ls.parity; tile_no = ls.tile_no;
+                if (kProf) { t_full += pr[0]; t_batch += pr[1]; }
+            } else {
+                if (op.two) mega_consume_mma<true, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
+                else mega_consume_mma<false, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
+            }
         } else {
-            if (op.np == 1) mega_consume<false, 1, kProf>(gp, p, k, sh, rp, tile_no, w, t_full, t_batch);
-            else mega_consume<false, 2, kProf>(gp, p, k, sh, rp, tile_no, w, t_full, t_batch);
+            if (op.np == 1) mega_consume<false, 1, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
+            else mega_consume<false, 2, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
         }
         tk_run[kk] += now() - trun0;
+        tk_batch[kk] += t_batch - tb_before;
+        tk_full[kk] += t_full - tf_before;
 
-        // ---- hand-off: the service warp publishes the operator after the tail of this CTA's last tile; a CTA that
+        // ---- hand-off: the tail warp publishes the operator after the tail of this CTA's last tile; a CTA that
         // owns no tile of it publishes here (its consumers have read whatever the prologue reads)
         if (my_tiles == 0) {
             if ((op.kind == MOP_PARTIAL || op.kind == MOP_CLS) && op.tp > 1) {
@@ -1207,7 +1513,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     if (kProf && p.prof && tid == 0) {
         long long* o = p.prof + (size_t)cta * 64;
         o[0] = now() - t_all0; o[1] = t_dep; o[2] = t_full; o[3] = t_batch; o[4] = t_attn; o[5] = t_pro;
-        for (int q = 0; q < 8; ++q) { o[8 + q] = tk_dep[q]; o[16 + q] = tk_pro[q]; o[24 + q] = tk_run[q]; }
+        for (int q = 0; q < 8; ++q) { o[8 + q] = tk_dep[q]; o[16 + q] = tk_pro[q]; o[24 + q] = tk_run[q]; o[40 + q] = tk_batch[q]; o[48 + q] = tk_full[q]; }
+    }
     }
 }
 

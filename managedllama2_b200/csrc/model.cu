@@ -174,6 +174,9 @@ struct Model {
     bool use_mega = true;
     bool mega_built = false, mega_ok = false;
     MegaOp* mega_ops = nullptr;
+    MegaTile* mega_tiles = nullptr;         // every CTA's tile descriptors, in streaming order
+    int* mega_tile_begin = nullptr;         // [grid + 1]
+    unsigned short* mega_op_tiles = nullptr;   // [nops][grid]
     unsigned int* mega_done = nullptr;
     int mega_nops = 0, mega_nstage = 0, mega_slot = 0, mega_att_bytes = 0, mega_smem = 0, mega_grid = 0;
     unsigned int mega_seq = 0;
@@ -442,6 +445,32 @@ static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, int nmat, bool
     };
     op.gran = std::max(rows_for_16(op.wrow), std::max(op.zrow ? rows_for_16(op.zrow) : 1, op.srow ? rows_for_16(op.srow) : 1));
     if (cols % op.gran) return false;
+    const int nruns = paired ? 2 : 1;
+    auto a16 = [](int b) { return (b + 15) & ~15; };
+    auto tile_bytes = [&](int units) { return nruns * (units * op.wrow + a16(units * op.zrow) + a16(units * op.srow)); };
+    auto set_layout = [&](int rmax) {
+        op.rmax = rmax;
+        op.off_z = rmax * op.wrow;
+        op.off_s = op.off_z + a16(rmax * op.zrow);
+        op.run_bytes = op.off_s + a16(rmax * op.srow);
+    };
+    if (fmt == 0) {
+        // int4 on the tensor cores: every working warp takes `np` whole quantisation groups of all rows of a tile; a
+        // full tile is one or two blocks of 8 rows (SwiGLU: 8 gate rows and the 8 matching up rows)
+        if (rows % kGroup) return false;
+        op.ngrp = rows / kGroup;
+        op.np = std::max(2, ceil_div(op.ngrp, kMegaConsumerWarps));   // two groups per warp keep the inputs in registers
+        op.kw = ceil_div(op.ngrp, op.np);
+        op.groups = 1;
+        op.tab_n = (op.ngrp * 4 + 7) & ~7;
+        int rmax = 0;
+        for (int r = paired ? 8 : 16; r >= 8 && !rmax; r -= 8)
+            if (r % op.gran == 0 && tile_bytes(r) <= slot_bytes) rmax = r;
+        if (!rmax) return false;
+        op.two = (paired || rmax == 16) ? 1 : 0;
+        set_layout(rmax);
+        return true;
+    }
     // Lane mapping: a group of kw warps spans a row with np weight vectors per lane; G groups share every tile. The
     // best mapping keeps the most lanes busy: (row coverage) x (warps in a group).
     op.kw = 0;
@@ -461,9 +490,6 @@ static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, int nmat, bool
     if (op.kw == 0) return false;
     // Rows of a full tile: whole batches for every group (a batch is 4 / np physical rows of a group), whole granules,
     // at most kMegaGroupRows physical rows per group, and the tile has to fit the slot.
-    const int nruns = paired ? 2 : 1;
-    auto a16 = [](int b) { return (b + 15) & ~15; };
-    auto tile_bytes = [&](int units) { return nruns * (units * op.wrow + a16(units * op.zrow) + a16(units * op.srow)); };
     const int batch_units = std::max(1, (4 / op.np) / nruns);
     int step = op.groups * batch_units;
     step = step / std::__gcd(step, op.gran) * op.gran;
@@ -475,11 +501,59 @@ static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, int nmat, bool
         for (int r = op.gran; r <= cap_units && tile_bytes(r) <= slot_bytes; r += op.gran) rmax = r;
     }
     if (rmax == 0) return false;
-    op.rmax = rmax;
-    op.off_z = rmax * op.wrow;
-    op.off_s = op.off_z + a16(rmax * op.zrow);
-    op.run_bytes = op.off_s + a16(rmax * op.srow);
+    op.tab_n = op.kw * 32 * op.np;
+    set_layout(rmax);
     return true;
+}
+
+// The tiles of operator k on one CTA, appended to `out`. The operator's output rows (QKV: the rows of q, k and v one
+// after the other) are cut into contiguous, balanced ranges of alignment granules, one per CTA (which CTAs get one granule
+// more rotates from operator to operator). A range is streamed as full tiles followed by one remainder tile; a tile never
+// spans two matrices. (int4: every tile costs the arithmetic of a full one, or of half a one up to 8 rows, so a range is
+// best cut into as few tiles as possible.)
+static void mega_tiles_of(const MegaOp& op, int k, int cta, int ncta, std::vector<MegaTile>& out)
+{
+    const int nseg = op.paired ? 1 : op.nmat, nruns = op.paired ? 2 : 1;
+    const size_t first = out.size();
+    const bool shared_counter = (op.kind == MOP_PARTIAL || op.kind == MOP_CLS) && op.tp > 1;
+    const int c = (cta + op.rot) % ncta;
+    const long long G = (long long)op.ngran * nseg;   // granules of all segments
+    const long long g0 = c * G / ncta, g1 = (c + 1) * G / ncta;
+    for (int seg = 0; seg < nseg; ++seg) {
+        const long long s0 = std::max<long long>(g0, (long long)seg * op.ngran), s1 = std::min<long long>(g1, (long long)(seg + 1) * op.ngran);
+        if (s1 <= s0) continue;
+        int row = (int)(s0 - (long long)seg * op.ngran) * op.gran;
+        int left = (int)(s1 - s0);   // granules
+        while (left > 0) {
+            const int ng = std::min(left, op.gmax);
+            const int n = ng * op.gran;
+            MegaTile T{};
+            T.row = row;
+            T.n = n;
+            T.info = (uint32_t)k | ((uint32_t)seg << 16) | ((op.kind == MOP_QKV && seg > 0) ? kTileCacheRow : 0u);
+            T.out = op.out[op.kind == MOP_QKV ? seg : 0];
+            T.opbits = (uint32_t)op.kind | (op.paired ? 8u : 0u) | (op.fmt == 0 ? 16u : 0u) | (shared_counter ? 32u : 0u) |
+                       ((uint32_t)op.kw << 8) | ((uint32_t)op.groups << 16);
+            for (int r = 0; r < nruns; ++r) {
+                const QWPtrs& q = op.mat[op.paired ? r : seg];
+                const unsigned char* src[3] = {reinterpret_cast<const unsigned char*>(q.w), reinterpret_cast<const unsigned char*>(q.z),
+                                               reinterpret_cast<const unsigned char*>(q.s)};
+                const int row_bytes[3] = {op.wrow, op.zrow, op.srow}, dst[3] = {0, op.off_z, op.off_s};
+                for (int part = 0; part < 3; ++part) {
+                    if (!src[part] || !row_bytes[part]) continue;
+                    MegaTileCopy& e = T.cp[r * 3 + part];
+                    e.src = src[part] + (size_t)row * row_bytes[part];
+                    e.bytes = (uint32_t)(n * row_bytes[part]);
+                    e.dst = (uint32_t)(r * op.run_bytes + dst[part]);
+                    T.total_bytes += e.bytes;
+                }
+            }
+            out.push_back(T);
+            row += n;
+            left -= ng;
+        }
+    }
+    if (out.size() > first) out.back().info |= kTileLast;
 }
 
 // Layout of the peer-visible communication buffer of one rank (tensor parallel persistent kernel).
@@ -511,7 +585,6 @@ static int build_mega(Model* m)
     const ml2_config& c = m->cfg;
     const int dim = c.dim, hs = m->head_size;
     if (m->heads_local > m->ctx->sm_count || hs != kHeadMax || m->tp > 8) return ML2_OK;
-    if ((long long)std::max(c.vocab_size, std::max(c.hidden_dim, dim)) * (m->ctx->sm_count + 1) >= (1ll << 23)) return ML2_OK;   // tile arithmetic in exact floats
     if (dim > 8 * kMegaNormVecs * kMegaConsThreads) return ML2_OK;   // a normalised input vector is held in registers by the CTA
     const CommLayout CL = comm_layout(m);
     auto peer = [&](int q, size_t off) { return static_cast<unsigned char*>(m->comm_peer[q]) + off; };
@@ -538,11 +611,9 @@ static int build_mega(Model* m)
             op.rot = rot % m->ctx->sm_count;
             rot += 37;   // the CTAs that own one granule more than the others change from operator to operator
             op.seg_rot = m->ctx->sm_count / 3 + 1;
-            op.inv_ncta = 1.0f / (float)m->ctx->sm_count;
             if (op.has_tiles) {
                 op.ngran = op.cols / op.gran;
                 op.gmax = op.rmax / op.gran;
-                op.inv_gmax = 1.0f / (float)op.gmax;
             }
             ops.push_back(op);
         };
@@ -643,8 +714,8 @@ static int build_mega(Model* m)
     int scratch = c.seq_len * 4 + kMegaConsumerWarps * kHeadMax * 4;
     for (const MegaOp& op : ops) {
         if (!op.has_tiles) continue;
-        const int tab_n = op.kw * 32 * op.np;
-        scratch = std::max(scratch, op.fmt == 0 ? tab_n * 5 * 16 : tab_n * 16);
+        const int tab_n = op.tab_n;
+        scratch = std::max(scratch, op.fmt == 0 ? tab_n * 4 * 16 + (tab_n / 4) * 16 : tab_n * 16);
         if (op.pro != 0 && (op.fmt == 0 ? tab_n * 4 : tab_n) > kMegaNormVecs * kMegaConsThreads) return ML2_OK;
     }
     scratch = (scratch + 127) & ~127;
@@ -681,9 +752,40 @@ static int build_mega(Model* m)
     int per_sm = 0;
     ML2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_token_kernel<false>, kMegaThreads, m->mega_smem));
     if (per_sm < 1) return ML2_OK;
+    if (ops.size() > 0xffffu) return ML2_OK;
     if (m->mega_ops) { cudaFree(m->mega_ops); m->mega_ops = nullptr; }
     ML2_CUDA(cudaMalloc(&m->mega_ops, ops.size() * sizeof(MegaOp)));
     ML2_CUDA(cudaMemcpyAsync(m->mega_ops, ops.data(), ops.size() * sizeof(MegaOp), cudaMemcpyHostToDevice, m->stream));
+    // every CTA's tile list and its tile counts per operator
+    {
+        const int ncta = m->mega_grid;
+        std::vector<MegaTile> tiles;
+        std::vector<int> begin(ncta + 1, 0);
+        std::vector<unsigned short> per_op(ops.size() * (size_t)ncta, 0);
+        for (int c = 0; c < ncta; ++c) {
+            begin[c] = (int)tiles.size();
+            for (size_t k = 0; k < ops.size(); ++k) {
+                if (!ops[k].has_tiles) continue;
+                const size_t before = tiles.size();
+                mega_tiles_of(ops[k], (int)k, c, ncta, tiles);
+                if (tiles.size() - before > 0xffffu) return ML2_OK;
+                per_op[k * ncta + c] = (unsigned short)(tiles.size() - before);
+            }
+        }
+        begin[ncta] = (int)tiles.size();
+        for (const MegaTile& T : tiles)
+            for (const MegaTileCopy& e : T.cp)
+                if ((reinterpret_cast<uintptr_t>(e.src) & 15u) || (e.bytes & 15u) || (e.dst & 15u)) return ML2_OK;   // bulk copies: 16-byte rule
+        if (m->mega_tiles) { cudaFree(m->mega_tiles); m->mega_tiles = nullptr; }
+        if (m->mega_tile_begin) { cudaFree(m->mega_tile_begin); m->mega_tile_begin = nullptr; }
+        if (m->mega_op_tiles) { cudaFree(m->mega_op_tiles); m->mega_op_tiles = nullptr; }
+        ML2_CUDA(cudaMalloc(&m->mega_tiles, std::max<size_t>(1, tiles.size()) * sizeof(MegaTile)));
+        ML2_CUDA(cudaMalloc(&m->mega_tile_begin, begin.size() * sizeof(int)));
+        ML2_CUDA(cudaMalloc(&m->mega_op_tiles, per_op.size() * sizeof(unsigned short)));
+        ML2_CUDA(cudaMemcpy(m->mega_tiles, tiles.data(), tiles.size() * sizeof(MegaTile), cudaMemcpyHostToDevice));
+        ML2_CUDA(cudaMemcpy(m->mega_tile_begin, begin.data(), begin.size() * sizeof(int), cudaMemcpyHostToDevice));
+        ML2_CUDA(cudaMemcpy(m->mega_op_tiles, per_op.data(), per_op.size() * sizeof(unsigned short), cudaMemcpyHostToDevice));
+    }
     if (tp) {
         m->mega_done_ptr = reinterpret_cast<unsigned int*>(peer(m->rank, CL.done_off));   // zeroed when the buffer was made
     } else {
@@ -706,6 +808,9 @@ static int forward_mega(Model* m, int pos, int next_pos, int write_token)
     MegaParams prm{};
     prm.ops = m->mega_ops;
     prm.nops = m->mega_nops;
+    prm.tiles = m->mega_tiles;
+    prm.tile_begin = m->mega_tile_begin;
+    prm.op_tiles = m->mega_op_tiles;
     prm.done = m->mega_done_ptr;
     prm.status = m->ctx->status_dev;
     prm.rope_table = m->rope_table;
@@ -876,6 +981,9 @@ int ml2_model_destroy(ml2_model* h)
         if (m->comm_attached && q != m->rank && m->comm_peer[q]) cudaIpcCloseMemHandle(m->comm_peer[q]);
     if (m->comm_local) cudaFree(m->comm_local);
     if (m->mega_ops) cudaFree(m->mega_ops);
+    if (m->mega_tiles) cudaFree(m->mega_tiles);
+    if (m->mega_tile_begin) cudaFree(m->mega_tile_begin);
+    if (m->mega_op_tiles) cudaFree(m->mega_op_tiles);
     if (m->mega_done) cudaFree(m->mega_done);
     for (void* p : m->owned) cudaFree(p);
     if (m->ctx->stream == m->stream) m->ctx->stream = nullptr;
