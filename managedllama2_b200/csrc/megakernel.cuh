@@ -518,7 +518,7 @@ __device__ __forceinline__ void mega_consume(const MegaOp* __restrict__ gp, cons
         const int bufo = buf * kRedBuf;
         // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
         float resid = 0.f;
-        const bool res_lane = xres != nullptr && kw_id == 0 && lane < cnt;
+        const bool res_lane = xres != nullptr && kw_id == 0 && lane < cnt && *w.abort_flag == 0u;
         if (res_lane) resid = __half2float(__ldcg(xres + rb + lane * G));
         const uint32_t sbase = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes;
         uint32_t bw = sbase + w_lane, bz = sbase + z_lane, bs = sbase + s_lane;
@@ -641,7 +641,7 @@ __device__ __forceinline__ void mega_consume_mma(const MegaOp* __restrict__ gp, 
         // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
         float resid = 0.f;
         bool res_lane = false;
-        if (xres != nullptr) {
+        if (xres != nullptr && *w.abort_flag == 0u) {   // (not once a wait has run out: the slot's row and size may be stale)
             res_lane = lane < sh.tile_n[rp.slot];
             if (res_lane) resid = __half2float(__ldcg(xres + sh.tile_row[rp.slot] + lane));
         }
@@ -869,7 +869,7 @@ __device__ __noinline__ MegaLoopState mega_consume_mma_reg(const MegaOp* __restr
         if (kProf) t_full += tb0 - tw0;
         const uint32_t bufo = (tile_no & (uint32_t)(kMegaRedBufs - 1)) * kRedBufBytes;
         // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
-        if (xres != nullptr) {
+        if (xres != nullptr && lds_u32(a.wait + 16u) == 0u) {   // (not once a wait has run out: the slot's row and size may be stale)
             const int n = (int)lds_u32(a.tile_n + (uint32_t)slot * 4u);
             if (lane < n) {
                 const int row = (int)lds_u32(a.tile_row + (uint32_t)slot * 4u);
@@ -1036,6 +1036,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 }
             }
             __syncwarp();
+            // some wait of this CTA ran out: the tiles that follow may never have been issued (no descriptor, no partial
+            // sums); nothing is stored or published any more
+            if (s_abort) break;
             const long long ts0 = now();
             tf_wait += ts0 - tw0;
             const int buf = i & (kMegaRedBufs - 1);
