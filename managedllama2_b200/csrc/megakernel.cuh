@@ -51,8 +51,8 @@ struct MegaOp {
     int rmax;                // units (rows, or row pairs) of a full tile
     int off_z, off_s, run_bytes;   // shared-memory layout of one run (the rows of one matrix in a tile)
     int has_tiles;           // weight operator
-    int rot, seg_rot;        // rotation of the CTA -> row range assignment, per operator and per segment
-    int ngran, gmax;         // granules of a segment (cols / gran), granules of a full tile (rmax / gran)
+    int rot;                 // rotation of the CTA -> row range assignment (host)
+    int ngran, gmax;         // granules of a segment (cols / gran), granules of a full tile (rmax / gran) (host)
     int tp;                  // ranks summed into the input (pro 3) / receiving the output (MOP_PARTIAL, sharded MOP_CLS)
     int out_row0;            // sharded classifier: first vocabulary row of this rank
     int att_layer;           // layer index (the split-attention counters advance once per layer and token)
@@ -240,9 +240,9 @@ struct MegaShared {
     unsigned char* table;
     uint64_t* full_bar;
     uint64_t* empty_bar;
-    float* red;               // [kMegaRedBufs][kMegaConsumerWarps][kMegaGroupRows]
+    float* red;               // [kMegaRedBufs][kMegaConsumerWarps][kMegaRedRows] partial sums of the tiles in flight
     float* part;              // [2][kMegaConsumerWarps] sum-of-squares partials
-    float* resid;             // [kMegaRedBufs][kMegaMaxGroups][kMegaGroupRows] residual values of the tiles in flight
+    float* resid;             // [kMegaRedBufs][kMegaRedRows] residual values of the tiles in flight (int4 operators)
     const int* tile_row;      // [nstage] first unit of the tile in each slot ...
     const int* tile_n;        // ... and its units (written by the copy warp before the slot's copies)
 };
@@ -274,101 +274,39 @@ __device__ __forceinline__ void mega_table_store_int4(uint4* tab, int tab_n, int
     if ((i & 15) == 0) tab[4 * tab_n + (i >> 4)] = make_uint4(__float_as_uint(-(1024.f * ev + 64.f * od)), __float_as_uint(ev + od), 0u, 0u);
 }
 
-struct MegaSlice {
-    uint32_t xp[16];
-    float a0, b0, c1g;
-};
-
-template <bool INT4>
-__device__ __forceinline__ void mega_load_slice(uint32_t tab, int tab_n, int u, MegaSlice& x)
-{
-    if (INT4) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            const uint4 t = lds_v4(tab + (uint32_t)(v * tab_n + u) * 16u);
-            x.xp[4 * v] = t.x; x.xp[4 * v + 1] = t.y; x.xp[4 * v + 2] = t.z; x.xp[4 * v + 3] = t.w;
-        }
-        const uint4 c = lds_v4(tab + (uint32_t)(4 * tab_n + u) * 16u);
-        x.a0 = __uint_as_float(c.x); x.b0 = __uint_as_float(c.y); x.c1g = __uint_as_float(c.z);
-    } else {
-        const uint4 t = lds_v4(tab + (uint32_t)u * 16u);
-        x.xp[0] = t.x; x.xp[1] = t.y; x.xp[2] = t.z; x.xp[3] = t.w;
-        x.a0 = x.b0 = x.c1g = 0.f;
-    }
-}
-
-// one 16-byte weight vector against the lane's prepared inputs
-template <bool INT4>
-__device__ __forceinline__ float mega_item(const uint4& wv, const MegaSlice& x)
+// ---- fp16 operator (the classifier): arithmetic of one batch -------------------------------------------------------
+// one 16-byte weight vector (8 fp16 weights) against the 8 matching inputs
+__device__ __forceinline__ float mega_item_f16(const uint4& wv, const uint4& x)
 {
 #ifdef ML2_DIAG_NOMATH
-    return __uint_as_float(wv.x ^ x.xp[0]);   // pipeline probe: loads stay, arithmetic goes
+    return __uint_as_float(wv.x ^ x.x);   // pipeline probe: loads stay, arithmetic goes
 #endif
-    if (INT4) {
-        float A = x.a0, B = x.b0, D = 0.f;
-        word_dot(wv.x, x.xp + 0, A, B, D);
-        word_dot(wv.y, x.xp + 4, A, B, D);
-        word_dot(wv.z, x.xp + 8, A, B, D);
-        word_dot(wv.w, x.xp + 12, A, B, D);
-        return fmaf(B, 0.0625f, A) + D;
-    } else {
-        float a = 0.f, b = 0.f;
-        a = fma_f16_f32(lo16(wv.x), lo16(x.xp[0]), a);
-        b = fma_f16_f32(hi16(wv.x), hi16(x.xp[0]), b);
-        a = fma_f16_f32(lo16(wv.y), lo16(x.xp[1]), a);
-        b = fma_f16_f32(hi16(wv.y), hi16(x.xp[1]), b);
-        a = fma_f16_f32(lo16(wv.z), lo16(x.xp[2]), a);
-        b = fma_f16_f32(hi16(wv.z), hi16(x.xp[2]), b);
-        a = fma_f16_f32(lo16(wv.w), lo16(x.xp[3]), a);
-        b = fma_f16_f32(hi16(wv.w), hi16(x.xp[3]), b);
-        return a + b;
-    }
+    float a = 0.f, b = 0.f;
+    a = fma_f16_f32(lo16(wv.x), lo16(x.x), a);
+    b = fma_f16_f32(hi16(wv.x), hi16(x.x), b);
+    a = fma_f16_f32(lo16(wv.y), lo16(x.y), a);
+    b = fma_f16_f32(hi16(wv.y), hi16(x.y), b);
+    a = fma_f16_f32(lo16(wv.z), lo16(x.z), a);
+    b = fma_f16_f32(hi16(wv.z), hi16(x.z), b);
+    a = fma_f16_f32(lo16(wv.w), lo16(x.w), a);
+    b = fma_f16_f32(hi16(wv.w), hi16(x.w), b);
+    return a + b;
 }
 
-// ---- arithmetic of one batch: four (row, vector) items of this lane -------------------------------------------------
-// Item i = row (i / NP) of the batch, weight vector (i % NP) of the lane. After the dot products a transposing
-// reduction inside each quad of lanes (= one quantisation group) leaves item j's group sum on lane j of the quad,
-// which applies that row's zero point and scale ONCE (instead of every lane for every row); the quads are then
-// summed. Returns the warp's row totals: row r on the lanes with ((lane & 3) / NP) == r.
-// NP == 1: the lane's slice `xs0` stays in registers for the whole operator. NP == 2: both slices are reloaded from
-// the table in shared memory for every batch (two of them do not fit the register budget of a 704-thread CTA).
+// A batch is four (row, vector) items of this lane: item i = row (i / NP) of the batch, weight vector (i % NP) of the
+// lane. Returns the warp's row totals: row r on the lanes with ((lane & 3) / NP) == r.
 //   wa[r]   shared-memory address of this lane's first weight vector in row r of the batch
 //   du      byte distance to the lane's second vector (NP == 2)
-//   za, sa  addresses of the zero word and the scale that THIS lane applies (its item's row and quantisation group)
-template <bool INT4, int NP>
-__device__ __forceinline__ float mega_batch(const MegaSlice& xs0, uint32_t tab, int tab_n, int u0, int u1, const uint32_t (&wa)[4 / NP],
-                                            uint32_t du, uint32_t za, uint32_t sa, int zshift, int nitems, int lane)
+template <int NP>
+__device__ __forceinline__ float mega_batch_f16(const uint4 (&xs)[NP], const uint32_t (&wa)[4 / NP], uint32_t du, int nitems, int lane)
 {
-    constexpr int NR = 4 / NP;
     uint4 wv[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) wv[i] = lds_v4(wa[i / NP] + ((i % NP) ? du : 0u));
-    uint32_t zw = 0;
-    unsigned short sc = 0;
-    if (INT4) {
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw) : "r"(za));
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc) : "r"(sa));
-    }
     float t[4] = {0.f, 0.f, 0.f, 0.f};
-    float cg;
-    if (NP == 1) {
-        cg = xs0.c1g;
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            if (i < nitems) t[i] = mega_item<INT4>(wv[i], xs0);   // warp-uniform: a short last batch costs only the rows it has
-    } else {
-        float cq[NP];
-#pragma unroll
-        for (int q = 0; q < NP; ++q) {
-            MegaSlice x;
-            mega_load_slice<INT4>(tab, tab_n, q ? u1 : u0, x);
-            cq[q] = x.c1g;
-#pragma unroll
-            for (int r = 0; r < NR; ++r)
-                if (r * NP + q < nitems) t[r * NP + q] = mega_item<INT4>(wv[r * NP + q], x);
-        }
-        cg = (lane & 1) ? cq[NP - 1] : cq[0];
-    }
+    for (int i = 0; i < 4; ++i)
+        if (i < nitems) t[i] = mega_item_f16(wv[i], xs[i % NP]);   // warp-uniform: a short last batch costs only the rows it has
     // 4 x 4 transposing reduction inside the quad: lane j of the quad ends with the quad's sum of item j
     const bool b2 = (lane & 2) != 0, b1 = (lane & 1) != 0;
     const float s0 = b2 ? t[0] : t[2], k0 = b2 ? t[2] : t[0];
@@ -377,10 +315,6 @@ __device__ __forceinline__ float mega_batch(const MegaSlice& xs0, uint32_t tab, 
     const float q1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 2);
     const float sn = b1 ? q0 : q1, kp = b1 ? q1 : q0;
     float v = kp + __shfl_xor_sync(0xffffffffu, sn, 1);
-    if (INT4) {
-        const float zf = (float)((zw >> zshift) & 0xFu);
-        v = half_bits_to_float(sc) * fmaf(-zf, cg, v);
-    }
     if (NP == 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 4);
     v += __shfl_xor_sync(0xffffffffu, v, 8);
@@ -447,96 +381,68 @@ __device__ __forceinline__ void mega_skip_tiles(MegaRing& rp, uint32_t& tile_no,
     rp.parity ^= (uint32_t)wraps & 1u;
 }
 
-// ---- consumer side of one weight operator ---------------------------------------------------------------------------
-// Everything that does not change from tile to tile is worked out once per operator; a tile costs a wait, the batches,
-// an arrival, the group's barrier and (first warp of the group) the tail.
-template <bool INT4, int NP, bool kProf>
-__device__ __forceinline__ void mega_consume(const MegaOp* __restrict__ gp, const MegaParams& p, int k, const MegaShared& sh, MegaRing& rp,
-                                             uint32_t& tile_no, const MegaWait& w, int my_tiles, long long& t_full, long long& t_batch)
+// ---- consumer side of the fp16 operator ------------------------------------------------------------------------------
+// Groups of `kw` warps span a weight row (a lane owns one or two 16-byte vectors of every row, its inputs stationary in
+// registers); all groups share a tile: group g takes rows g, g + G, ... of it. Everything that does not change from tile
+// to tile is worked out once per operator; a tile costs a wait, the batches and an arrival. The partial sums of a tile
+// wait for the tail warp in one of kMegaRedBufs buffers (a warp is at most `nstage` tiles ahead of the tail).
+template <int NP, bool kProf>
+__device__ __forceinline__ void mega_consume_f16(const MegaOp* __restrict__ gp, const MegaParams& p, int k, const MegaShared& sh, MegaRing& rp,
+                                                 uint32_t& tile_no, const MegaWait& w, int my_tiles, long long& t_full, long long& t_batch)
 {
     constexpr int NR = 4 / NP;
     const int tid = (int)threadIdx.x - kMegaServiceThreads, lane = tid & 31, warp = tid >> 5;
-    const int G = gp->groups, kw = gp->kw, kind = gp->kind;
-    const bool paired = gp->paired != 0;
+    const int G = gp->groups, kw = gp->kw;
     const int group = warp / kw, kw_id = warp - group * kw;
-    const bool in_group = group < G;
-    const int kw32 = kw * 32, tab_n = kw32 * NP, units = gp->units;
-    const uint32_t tab = smem_u32(sh.table);
-    const int u0 = kw_id * 32 + lane, u1 = u0 + kw32;
-
-    // NP == 1: this lane's slice is stationary in registers for the whole operator
-    MegaSlice xs0;
-    if (NP == 1) mega_load_slice<INT4>(tab, tab_n, u0, xs0);
-    // arrival weight on a slot's empty barrier: the working warps of the operator add up to the barrier's fixed count
-    const uint32_t my_arrive = (warp == 0) ? (kMegaBarCount - (uint32_t)(G * kw) + 1u) : 1u;
-
-    const uint32_t wrow = (uint32_t)gp->wrow, zrow = (uint32_t)gp->zrow, srow = (uint32_t)gp->srow;
-    const uint32_t run_bytes = (uint32_t)gp->run_bytes;
-    // slots past the end of a row hold zero inputs; their addresses are clamped into the row
-    const int ua0 = u0 < units ? u0 : units - 1, ua1 = u1 < units ? u1 : units - 1;
-    // byte offsets inside a slot of this lane's first weight vector in the group's first row, and from row to row
-    const uint32_t gw = (uint32_t)G * wrow, gz = (uint32_t)G * zrow, gs = (uint32_t)G * srow;
-    const uint32_t w_lane = (uint32_t)group * wrow + (uint32_t)ua0 * 16u;
-    const uint32_t du = (uint32_t)(ua1 - ua0) * 16u;
-    // rows 1 .. 3 of a batch relative to its row 0 (paired: gate, up, next gate, next up)
-    const uint32_t ro1 = paired ? run_bytes : gw, ro2 = paired ? gw : 2u * gw, ro3 = paired ? gw + run_bytes : 3u * gw;
-    const uint32_t adv_w = (paired ? (uint32_t)(NR / 2) : (uint32_t)NR) * gw;
-    const uint32_t adv_z = (paired ? (uint32_t)(NR / 2) : (uint32_t)NR) * gz, adv_s = (paired ? (uint32_t)(NR / 2) : (uint32_t)NR) * gs;
-    // the zero word and scale this lane applies: item j = lane & 3 of the quad -> row j / NP of the batch, vector j % NP
-    const int rj = (lane & 3) / NP;
-    const int gj = (((lane & 3) % NP) ? ua1 : ua0) >> 2;   // quantisation group of that vector
-    const uint32_t rz = paired ? (uint32_t)(rj & 1) * run_bytes + (uint32_t)(rj >> 1) * gz : (uint32_t)rj * gz;
-    const uint32_t rs = paired ? (uint32_t)(rj & 1) * run_bytes + (uint32_t)(rj >> 1) * gs : (uint32_t)rj * gs;
-    const uint32_t z_lane = (uint32_t)gp->off_z + (uint32_t)group * zrow + rz + (uint32_t)(gj >> 3) * 4u;
-    const uint32_t s_lane = (uint32_t)gp->off_s + (uint32_t)group * srow + rs + (uint32_t)gj * 2u;
-    const int zshift = (gj & 7) * 4;
-    const bool storer = lane < 4 && (lane % NP) == 0;     // lane r * NP of quad 0 stores row r of a batch
-    const int recipG = (65536 + G - 1) / G;                // x / G for the small x that occur below
-    float* const red_w = sh.red + warp * kMegaRedRows + (lane & 3) / NP;
-    constexpr int kRedBuf = kMegaConsumerWarps * kMegaRedRows;
-    static_assert((kMegaRedBufs & (kMegaRedBufs - 1)) == 0 && kMegaRedBufs >= kMegaMaxStages + 2, "partial buffers");
-
-    const uint32_t ring = smem_u32(sh.ring);
-
-    // The tail of a tile (sum over the k-warps, rounding, store) belongs to the tail warp, which runs it when every
-    // consumer warp has arrived on the slot's empty barrier: a consumer never blocks on a sibling. The partial sums wait
-    // in one of kMegaRedBufs buffers (a warp is at most `nstage` tiles ahead of the tail).
-    const __half* const xres = (kind == MOP_RESID) ? gp->out[0] : nullptr;
-    if (!in_group) {
+    if (group >= G) {
         mega_skip_tiles(rp, tile_no, my_tiles, p.nstage);
         return;
     }
+    const int kw32 = kw * 32, units = gp->units;
+    const uint32_t tab = smem_u32(sh.table);
+    const int u0 = kw_id * 32 + lane, u1 = u0 + kw32;
+    uint4 xs[NP];   // this lane's inputs: slots past the end of the row hold zeros in the table
+    xs[0] = lds_v4(tab + (uint32_t)u0 * 16u);
+    if (NP == 2) xs[NP - 1] = lds_v4(tab + (uint32_t)u1 * 16u);
+    // arrival weight on a slot's empty barrier: the working warps of the operator add up to the barrier's fixed count
+    const uint32_t my_arrive = (warp == 0) ? (kMegaBarCount - (uint32_t)(G * kw) + 1u) : 1u;
+    const uint32_t wrow = (uint32_t)gp->wrow;
+    // slots past the end of a row: their addresses are clamped into the row
+    const int ua0 = u0 < units ? u0 : units - 1, ua1 = u1 < units ? u1 : units - 1;
+    // byte offsets inside a slot of this lane's first weight vector in the group's first row, and from row to row
+    const uint32_t gw = (uint32_t)G * wrow;
+    const uint32_t w_lane = (uint32_t)group * wrow + (uint32_t)ua0 * 16u;
+    const uint32_t du = (uint32_t)(ua1 - ua0) * 16u;
+    const int rj = (lane & 3) / NP;
+    const bool storer = lane < 4 && (lane % NP) == 0;     // lane r * NP of quad 0 stores row r of a batch
+    const int recipG = (65536 + G - 1) / G;                // x / G for the small x that occur below
+    float* const red_w = sh.red + warp * kMegaRedRows + rj;
+    constexpr int kRedBuf = kMegaConsumerWarps * kMegaRedRows;
+    static_assert((kMegaRedBufs & (kMegaRedBufs - 1)) == 0 && kMegaRedBufs >= kMegaMaxStages + 2, "partial buffers");
+    const uint32_t ring = smem_u32(sh.ring);
+
     for (int ti = 0; ti < my_tiles; ++ti) {
         const long long tw0 = kProf ? clock64() : 0ll;
         mega_wait_bar(&sh.full_bar[rp.slot], rp.parity, w, 2u, k, 32u);
         if (kProf) t_full += clock64() - tw0;
-        const int n = sh.tile_n[rp.slot];                                          // units in this tile
-        const int rb = sh.tile_row[rp.slot] + group;                               // first row of this group
-        const int cnt = n > group ? ((n - group + G - 1) * recipG) >> 16 : 0;      // units of this group
-        const int nrows = paired ? 2 * cnt : cnt;                                  // physical rows of this group
-        const int buf = (int)(tile_no & (uint32_t)(kMegaRedBufs - 1));
-        const int bufo = buf * kRedBuf;
-        // residual values for the tail: fetched here (the consumers hold the operator's dependency), parked beside the partials
-        float resid = 0.f;
-        const bool res_lane = xres != nullptr && kw_id == 0 && lane < cnt && *w.abort_flag == 0u;
-        if (res_lane) resid = __half2float(__ldcg(xres + rb + lane * G));
-        const uint32_t sbase = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes;
-        uint32_t bw = sbase + w_lane, bz = sbase + z_lane, bs = sbase + s_lane;
-        for (int p0 = 0; p0 < nrows; p0 += NR, bw += adv_w, bz += adv_z, bs += adv_s) {
+        const int n = sh.tile_n[rp.slot];                                            // rows in this tile
+        const int nrows = n > group ? ((n - group + G - 1) * recipG) >> 16 : 0;      // rows of this group
+        const int bufo = (int)(tile_no & (uint32_t)(kMegaRedBufs - 1)) * kRedBuf;
+        uint32_t bw = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes + w_lane;
+        for (int p0 = 0; p0 < nrows; p0 += NR, bw += (uint32_t)NR * gw) {
             const int left = nrows - p0;
             uint32_t wa[NR];
             wa[0] = bw;
-            if (NR > 1) wa[1 % NR] = bw + (left > 1 ? ro1 : 0u);    // rows past the end repeat row 0 (not stored)
+            if (NR > 1) wa[1 % NR] = bw + (left > 1 ? gw : 0u);    // rows past the end repeat row 0 (not stored)
             if (NR > 2) {
-                wa[2 % NR] = bw + (left > 2 ? ro2 : 0u);
-                wa[3 % NR] = bw + (left > 3 ? ro3 : 0u);
+                wa[2 % NR] = bw + (left > 2 ? 2u * gw : 0u);
+                wa[3 % NR] = bw + (left > 3 ? 3u * gw : 0u);
             }
             const long long tb0 = kProf ? clock64() : 0ll;
-            const float v = mega_batch<INT4, NP>(xs0, tab, tab_n, u0, u1, wa, du, bz, bs, zshift, (left < NR ? left : NR) * NP, lane);
+            const float v = mega_batch_f16<NP>(xs, wa, du, (left < NR ? left : NR) * NP, lane);
             if (storer && rj < left) red_w[bufo + p0] = v;
             if (kProf) t_batch += clock64() - tb0;
         }
-        if (res_lane) sh.resid[(buf * kMegaMaxGroups + group) * kMegaGroupRows + lane] = resid;
         // last read of the slot and the partials of this warp are done: one arrival tells the copy and tail warps
         __syncwarp();
         if (lane == 0) mbar_arrive_n(&sh.empty_bar[rp.slot], my_arrive);
@@ -684,7 +590,7 @@ __device__ __forceinline__ void mega_consume_mma(const MegaOp* __restrict__ gp, 
             red_w[buf * kRedBuf] = tot_a;
             if (TWO) red_w[buf * kRedBuf + 8] = tot_b;
         }
-        if (res_lane) sh.resid[buf * (kMegaMaxGroups * kMegaGroupRows) + lane] = resid;
+        if (res_lane) sh.resid[buf * kMegaRedRows + lane] = resid;
         if (kProf) t_batch += clock64() - tb0;
         // last read of the slot and the partials of this warp are done: one arrival tells the copy and tail warps
         __syncwarp();
@@ -873,7 +779,7 @@ __device__ __noinline__ MegaLoopState mega_consume_mma_reg(const MegaOp* __restr
             const int n = (int)lds_u32(a.tile_n + (uint32_t)slot * 4u);
             if (lane < n) {
                 const int row = (int)lds_u32(a.tile_row + (uint32_t)slot * 4u);
-                sts_f32(a.resid + ((tile_no & (uint32_t)(kMegaRedBufs - 1)) * (uint32_t)(kMegaMaxGroups * kMegaGroupRows) + (uint32_t)lane) * 4u,
+                sts_f32(a.resid + ((tile_no & (uint32_t)(kMegaRedBufs - 1)) * (uint32_t)kMegaRedRows + (uint32_t)lane) * 4u,
                         __half2float(__ldcg(xres + row + lane)));
             }
         }
@@ -905,7 +811,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
     __shared__ __align__(8) uint64_t empty_bar[kMegaMaxStages];
     __shared__ float s_red[kMegaRedBufs * kMegaConsumerWarps * kMegaRedRows];
     __shared__ float s_part[2][kMegaConsumerWarps];
-    __shared__ float s_resid[kMegaRedBufs * kMegaMaxGroups * kMegaGroupRows];
+    __shared__ float s_resid[kMegaRedBufs * kMegaRedRows];
     __shared__ float s_att_tmp[kMegaConsumerWarps];
     __shared__ __align__(16) __half s_q[kHeadMax];
     __shared__ float s_best_v[kMegaConsumerWarps];
@@ -1077,7 +983,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 const long long te0 = now();
                 tf_epi -= te0 - ts0;
                 if (lane < n) {
-                    const float resid = (f_kind == MOP_RESID) ? s_resid[buf * (kMegaMaxGroups * kMegaGroupRows) + lane] : 0.f;
+                    const float resid = (f_kind == MOP_RESID) ? s_resid[buf * kMegaRedRows + lane] : 0.f;
                     mega_epilogue(f_gp, f_kind, f_out, row + lane, sa, sb, resid);
                 }
 #ifdef ML2_DIAG_NOTAIL
@@ -1085,17 +991,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
 #else
             } else {
 #endif
+                // fp16: unit j is row u of group g; the group's warps left its partial at row u
                 const int f_recipG = (65536 + f_G - 1) / f_G;
                 for (int j = lane; j < n; j += 32) {
-                    const int u = (j * f_recipG) >> 16, g = j - u * f_G;   // unit j is unit u of group g
-                    const float* rg = red + g * f_kw * kMegaRedRows + (f_paired ? 2 * u : u);
-                    float sa = 0.f, sb = 0.f;
-                    for (int q = 0; q < f_kw; ++q) {
-                        sa += rg[q * kMegaRedRows];
-                        if (f_paired) sb += rg[q * kMegaRedRows + 1];
-                    }
-                    const float resid = (f_kind == MOP_RESID) ? s_resid[(buf * kMegaMaxGroups + g) * kMegaGroupRows + u] : 0.f;
-                    mega_epilogue(f_gp, f_kind, f_out, row + j, sa, sb, resid);
+                    const int u = (j * f_recipG) >> 16, g = j - u * f_G;
+                    const float* rg = red + g * f_kw * kMegaRedRows + u;
+                    float sa = 0.f;
+                    for (int q = 0; q < f_kw; ++q) sa += rg[q * kMegaRedRows];
+                    mega_epilogue(f_gp, f_kind, f_out, row + j, sa, 0.f, 0.f);
                 }
             }
             const long long ts1 = now();
@@ -1490,8 +1393,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 else mega_consume_mma<false, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
             }
         } else {
-            if (op.np == 1) mega_consume<false, 1, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
-            else mega_consume<false, 2, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
+            if (op.np == 1) mega_consume_f16<1, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
+            else mega_consume_f16<2, kProf>(gp, p, k, sh, rp, tile_no, w, my_tiles, t_full, t_batch);
         }
         tk_run[kk] += now() - trun0;
         tk_batch[kk] += t_batch - tb_before;

@@ -432,7 +432,7 @@ static bool mega_plan_op(MegaOp& op, int fmt, int rows, int cols, int nmat, bool
         op.srow = ssize * 2;
         op.units = wsize / 4;
     } else {
-        if (rows % 8) return false;
+        if (rows % 8 || paired) return false;
         op.wrow = rows * 2;
         op.zrow = op.srow = 0;
         op.units = rows / 8;
@@ -610,7 +610,6 @@ static int build_mega(Model* m)
         auto push = [&](MegaOp& op) {
             op.rot = rot % m->ctx->sm_count;
             rot += 37;   // the CTAs that own one granule more than the others change from operator to operator
-            op.seg_rot = m->ctx->sm_count / 3 + 1;
             if (op.has_tiles) {
                 op.ngran = op.cols / op.gran;
                 op.gmax = op.rmax / op.gran;

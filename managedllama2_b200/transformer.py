@@ -75,7 +75,7 @@ def _qw_window(rows_full, ncols, g0, ngroups):
 
 
 def synthetic_weights(ctx, config, seed=31415, tp_size=1, tp_rank=0, sigma=0.02):
-    """Random-init model of BASELINE's construction, generated on the device shard by shard.
+    """Random-init model (nibbles uniform in 0..15, zero points near 8, scales about 0.01, fp16 normal elsewhere), generated on the device shard by shard.
 
     int4 weights and zero points uniform in [0,15], scales fp16 uniform in [0.001,0.02]; embeddings,
     classifier and norm weights fp16 ~ N(0, sigma^2). Values depend only on (seed, tensor id, logical

@@ -24,8 +24,15 @@ def build(force=False):
     return _LIB_PATH
 
 
-def build_ref(reference_root="/root/reference", force=False):
+def reference_root():
+    """Where the reference checkout lives: ML2_REFERENCE_ROOT, else a ``reference`` directory beside this repository."""
+    return os.environ.get("ML2_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def build_ref(reference_root=None, force=False):
     """Compiles the reference's own .cu files (in place, outputs into oracle/_ref/) if the checkout is there."""
+    if reference_root is None:
+        reference_root = globals()["reference_root"]()
     if not os.path.isdir(os.path.join(reference_root, "native")):
         return False
     if force or not os.path.exists(os.path.join(REF_DIR, "mat_vec_kernel.cubin")):

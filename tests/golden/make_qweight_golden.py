@@ -10,6 +10,7 @@ available:
 """
 import json
 import re
+import os
 import sys
 
 
@@ -35,6 +36,9 @@ def parse(path):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference checkout: first argument, else ML2_REFERENCE_ROOT, else a `reference` directory beside this repository
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("ML2_REFERENCE_ROOT") or
+                                                  os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference"))
     json.dump(parse(root + "/test/QWeightTestData.cs"), sys.stdout, separators=(",", ":"))
     sys.stdout.write("\n")

@@ -1,4 +1,4 @@
-"""Shared helpers for the parity tests: seeded inputs in the BASELINE distributions, device upload, error metric."""
+"""Shared helpers for the parity tests: seeded inputs in the value distributions of random-init AWQ weights (nibbles uniform, zeros near 8, scales about 0.01), device upload, error metric."""
 import numpy as np
 
 import oracle

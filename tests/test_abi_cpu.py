@@ -45,7 +45,7 @@ def test_config_struct_layout_matches_reference_header():
 
 
 def test_qweight_sizes_formula():
-    # src/QKVMatVec.cs:22-24 on the BASELINE shapes
+    # src/QKVMatVec.cs:22-24 on the benchmark shapes
     assert ml2.qweight_sizes(4096) == (512, 4, 32)
     assert ml2.qweight_sizes(5120) == (640, 5, 40)
     assert ml2.qweight_sizes(11008) == (1376, 11, 86)

@@ -2,9 +2,9 @@
 
 Mirrors test/MatVecInt4Tests.cs, QKVMatVecInt4Tests.cs, SwiGLUMatVecInt4Tests.cs and MatVecTests.cs of
 the reference, and adds what they leave out: non-zero zero points, realistic scales, multi-row matrices
-whose d_in is not a multiple of 1024, ragged output counts, BASELINE config 1 and 2 shapes.
+whose d_in is not a multiple of 1024, ragged output counts, the 4096 x 4096 and Llama-2-7B layer shapes.
 
-Tolerance (north star): relative error <= 1e-3 against the fp32-accumulate CPU arithmetic, measured as
+Tolerance: relative error <= 1e-3 against the fp32-accumulate CPU arithmetic, measured as
 |got-want| / max(|want|, rms(want)).
 """
 import numpy as np

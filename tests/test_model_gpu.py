@@ -4,7 +4,7 @@ The reference has no runnable model-level test (test/TransformerTests.cs:8-23 is
 checkpoint), so the arbiter is the oracle's forward (oracle/ml2_oracle.c: orc_forward), which follows
 src/Transformer.cs:158-190 with an fp16 store wherever the reference kernels store fp16.
 
-Tolerances (north star): logits within 1e-2 absolute of the reference arithmetic and identical greedy
+Tolerances: logits within 1e-2 absolute of the reference arithmetic and identical greedy
 tokens; here the logits are also held to 2e-2 relative to their own spread, which is much tighter.
 """
 import os
@@ -45,7 +45,7 @@ def test_synthetic_device_equals_host():
             assert np.array_equal(q.Zeros.cpu().numpy().view(np.uint32), H[key][1]), (l, name)
             assert np.array_equal(q.Scales.cpu().numpy().view(np.uint16), H[key][2].view(np.uint16)), (l, name)
         assert np.array_equal(L.rmsAttentionWeight.cpu().numpy().view(np.uint16), H["rms_att"].view(np.uint16))
-    # value distributions of the BASELINE construction
+    # value distributions of the random-init construction the benchmark uses
     s = hw["layers"][0]["q"][2].astype(np.float32)
     assert 0.00099 <= s.min() and s.max() <= 0.02001
     e = hw["embed"].astype(np.float32)

@@ -36,7 +36,7 @@ def test_qweight_fromdata_golden(golden_dir):
 
 
 def test_fixture_matches_reference_checkout(golden_dir):
-    ref = "/root/reference/test/QWeightTestData.cs"
+    ref = os.path.join(oracle.reference_root(), "test", "QWeightTestData.cs")
     if not os.path.exists(ref):
         pytest.skip("reference checkout not present")
     import importlib.util
