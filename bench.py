@@ -310,16 +310,21 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     dist = None
-    nccl_id = None
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+
+    def fresh_nccl_id():
+        """A unique id serves ONE communicator: every model gets its own, made on rank 0 and broadcast."""
+        if dist is None:
+            return None
         idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
             idt = torch.frombuffer(bytearray(ml2.Transformer.nccl_unique_id()), dtype=torch.uint8).cuda()
         dist.broadcast(idt, 0)
-        nccl_id = bytes(idt.cpu().numpy().tobytes())
+        return bytes(idt.cpu().numpy().tobytes())
+
     fused = os.environ.get("ML2_TP_FUSED", "1") == "1"
     ctx = ml2.CudaContext(local_rank)
 
@@ -343,7 +348,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         c2["numLayers"] = 2
         conf2 = ml2.Config(seqLength=16, **c2)
         w2 = ml2.synthetic_weights(ctx, conf2, seed=SEED + 1, tp_size=world, tp_rank=rank, sigma=1.0)
-        t2 = ml2.Transformer(conf2, w2, ctx, tp_size=world, tp_rank=rank, nccl_id=nccl_id)
+        t2 = ml2.Transformer(conf2, w2, ctx, tp_size=world, tp_rank=rank, nccl_id=fresh_nccl_id())
         if fused:
             t2.attach_peers_with(dist)
         toks = [11, 4242, 31999 % conf2.vocabSize, 77]
@@ -354,6 +359,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             cpu = oracle.CpuModel(oracle_cfg(c2, 16), ml2.synthetic_weights_host(conf2, seed=SEED + 1, sigma=1.0), mode=1)
         identical, max_err, ok = True, 0.0, True
         for pos in range(4):
+            dist.barrier()   # ranks launch a token together (rank 0 spends seconds in the CPU oracle between tokens)
             t2.Forward(pos, pos + 1, False)
             lg = t2.logits()
             t = torch.from_numpy(lg.view(np.int16).astype(np.int32)).cuda()
@@ -376,7 +382,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     seq_len = max(seq_len, max(PROMPT_LEN, args.context) + args.warmup + 2 * args.steps + 8)
     config = ml2.Config(seqLength=seq_len, **cfg)
     weights = ml2.synthetic_weights(ctx, config, seed=SEED, tp_size=world, tp_rank=rank)
-    tr = ml2.Transformer(config, weights, ctx, tp_size=world, tp_rank=rank, nccl_id=nccl_id)
+    tr = ml2.Transformer(config, weights, ctx, tp_size=world, tp_rank=rank, nccl_id=fresh_nccl_id())
     if dist is not None and fused:
         tr.attach_peers_with(dist)   # persistent kernel per GPU, all-reduce fused over peer memory
     sp = ctypes.c_void_p()

@@ -398,7 +398,7 @@ __device__ __forceinline__ void mega_consume_f16(const MegaOp* __restrict__ gp, 
         mega_skip_tiles(rp, tile_no, my_tiles, p.nstage);
         return;
     }
-    const int kw32 = kw * 32, units = gp->units;
+    const int kw32 = kw * 32, units = gp->units, rmax = gp->rmax;
     const uint32_t tab = smem_u32(sh.table);
     const int u0 = kw_id * 32 + lane, u1 = u0 + kw32;
     uint4 xs[NP];   // this lane's inputs: slots past the end of the row hold zeros in the table
@@ -425,7 +425,8 @@ __device__ __forceinline__ void mega_consume_f16(const MegaOp* __restrict__ gp, 
         const long long tw0 = kProf ? clock64() : 0ll;
         mega_wait_bar(&sh.full_bar[rp.slot], rp.parity, w, 2u, k, 32u);
         if (kProf) t_full += clock64() - tw0;
-        const int n = sh.tile_n[rp.slot];                                            // rows in this tile
+        // rows in this tile (none once a wait has run out: the slot's row count may then be another operator's)
+        const int n = *w.abort_flag ? 0 : min(sh.tile_n[rp.slot], rmax);
         const int nrows = n > group ? ((n - group + G - 1) * recipG) >> 16 : 0;      // rows of this group
         const int bufo = (int)(tile_no & (uint32_t)(kMegaRedBufs - 1)) * kRedBuf;
         uint32_t bw = ring + (uint32_t)rp.slot * (uint32_t)p.slot_bytes + w_lane;

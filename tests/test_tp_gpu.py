@@ -49,15 +49,19 @@ def test_tensor_parallel_from_model_bin(tmp_path):
     assert out.returncode == 0 and "TP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
-def test_late_rank_runs_into_the_wait_limit_and_recovers():
+@pytest.mark.parametrize("shape", ["small", "13b"])
+def test_late_rank_runs_into_the_wait_limit_and_recovers(shape):
     """Two ranks, one of them calls Forward 1.5 s late while the wait limit is 0.2 s: every rank gets ML2_E_DEVICE from a
     kernel that gave up waiting (no fault, the context stays usable), refuses the next forward, resets, and then decodes
-    the same tokens as the CPU oracle."""
+    the same tokens as the CPU oracle. Also on the benchmark's shape, where the roles of a CTA that has given up run
+    through tiles and rows that are much larger than whatever the ring last held."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "0"), ML2_TP_LATE="1")
+    if shape == "13b":
+        env["ML2_TP_SHAPE"] = "13b"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29631", os.path.join(here, "tp_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
