@@ -73,7 +73,7 @@ int ml2_ctx_set_stream(ml2_ctx* ctx, void* cuda_stream);
 int ml2_ctx_set_pdl(ml2_ctx* ctx, int enabled);
 int ml2_ctx_synchronize(ml2_ctx* ctx);
 /* Budget of every device-side wait (mbarrier phases, operator counters, peer counters), in SM clock
- * cycles; default 4e9 (about two seconds). A wait that runs out writes the error word and the kernel
+ * cycles; default 2e10 (about ten seconds). A wait that runs out writes the error word and the kernel
  * runs to its end; the next synchronising call returns ML2_E_DEVICE. No counterpart in the reference
  * (its kernels never wait on one another). */
 int ml2_ctx_set_wait_limit(ml2_ctx* ctx, long long sm_cycles);

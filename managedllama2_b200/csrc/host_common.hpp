@@ -19,7 +19,7 @@ struct Ctx {
     void* scratch = nullptr;          // host-buffer entry points stage their vectors here
     size_t scratch_bytes = 0;
     long long launches = 0;
-    long long wait_cycles = 4000000000ll;   // budget of every device-side wait, in SM clock cycles (about two seconds)
+    long long wait_cycles = 20000000000ll;   // budget of every device-side wait, in SM clock cycles (about ten seconds)
 };
 
 struct MatVecPlan {

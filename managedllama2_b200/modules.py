@@ -58,7 +58,7 @@ class CudaContext:
         _lib.check(self._lib.ml2_ctx_synchronize(self.handle))
 
     def set_wait_limit(self, sm_cycles):
-        """Budget of every device-side wait, in SM clock cycles (default about two seconds)."""
+        """Budget of every device-side wait, in SM clock cycles (default 2e10, about ten seconds)."""
         _lib.check(self._lib.ml2_ctx_set_wait_limit(self.handle, ctypes.c_longlong(int(sm_cycles))))
 
     def status(self):
