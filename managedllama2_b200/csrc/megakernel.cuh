@@ -119,15 +119,14 @@ struct MegaParams {
     long long* prof;           // optional [gridDim.x][64] cycle counters (diagnostics), may be null
 };
 
-constexpr int kMegaConsumerWarps = 21;   // 4 groups of 5, 3 of 7, 5 of 4, 2 of 10
-constexpr int kMegaServiceWarps = 2;     // copy warp and tail warp: the CTA's FIRST warps (the scheduler favours low warp numbers, and
-                                         // these two issue little but sit on every tile's critical path)
+constexpr int kMegaConsumerWarps = 21;   // 20 warps x 2 quantisation groups span a 5120-input row, 18 x 6 a 13824-input row
+constexpr int kMegaServiceWarps = 2;     // copy warp and tail warp: warps 0 and 1 of the CTA (first or last made no measurable difference)
 constexpr int kMegaServiceThreads = kMegaServiceWarps * 32;
 constexpr int kMegaWarps = kMegaConsumerWarps + kMegaServiceWarps;
 constexpr int kMegaThreads = kMegaWarps * 32;
 constexpr int kMegaConsThreads = kMegaConsumerWarps * 32;
 constexpr int kMegaMaxStages = 6;
-constexpr int kMegaMaxGroups = 8;     // named barriers 2 .. 9
+constexpr int kMegaMaxGroups = 8;     // groups of warps that may share a tile (fp16 weights)
 constexpr int kMegaGroupRows = 8;     // physical rows of one tile that one group may own (fp16 weights)
 constexpr int kMegaRedRows = 16;      // partial sums one warp may leave per tile
 constexpr int kMegaRedBufs = 8;       // tiles whose k-warp partials may be waiting for their tail (more than the ring depth + 1)
