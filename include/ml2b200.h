@@ -233,13 +233,21 @@ int ml2_model_comm_handle(ml2_model* model, void* out64);
 int ml2_model_comm_attach(ml2_model* model, const void* handles_rank_order, int n_ranks);
 /* Diagnostics: per-CTA cycle counters of the last persistent-kernel launch, 64 values per CTA ([0..5] total,
  * dependency waits, ring waits, cycles inside the arithmetic batches, attention, prologue; [8..31] wait / prologue /
- * tile cycles per operator kind; [32..35] copy warp and tail warp total and wait cycles); needs ML2_MEGA_PROF=1 in
+ * tile cycles per operator kind; [32..39] copy warp and tail warp: total and wait cycles, the tail's epilogue, sum,
+ * hand-back and publish cycles; [40..55] arithmetic and ring-wait cycles per operator kind); needs ML2_MEGA_PROF=1 in
  * the environment when the model is created. */
 int ml2_model_debug_prof(ml2_model* model, long long* out, int n);
 /* Diagnostics (failure-path test): makes the model expect one more round of operator arrivals than its counters
  * hold, as after a rank skipped a forward; the next forward's waits then run out after the wait limit, the kernel
  * returns, and the synchronising call reports ML2_E_DEVICE. Touches nothing on the device. */
 int ml2_model_debug_skip_launch(ml2_model* model);
+/* Diagnostics, host only (no GPU needed): plans one weight operator of the persistent kernel (fmt 0 int4, 1 fp16;
+ * `rows` inputs, `cols` outputs per matrix, `nmat` matrices, `paired` for gate / up) for a ring slot of `slot_bytes`
+ * and `n_cta` CTAs, builds every CTA's tile list as the model does and checks it: every output row covered exactly
+ * once, tiles inside the operator and no larger than a full tile, every bulk copy 16-byte aligned in source, size
+ * and destination and inside the slot. out8 = {planned, rows covered, fewest / most tiles of a CTA, violations,
+ * rows of a full tile, working warps, quantisation groups (fp16: weight vectors) per warp}. */
+int ml2_debug_tile_plan(int fmt, int rows, int cols, int nmat, int paired, int slot_bytes, int n_cta, long long* out8);
 /* Tuning: the sequence length from which the persistent kernel splits every head's attention over several CTAs
  * (default 704, the measured crossover on a B200 for the 13B shape; shorter sequences keep one CTA per head). */
 int ml2_model_set_split_attention_from(ml2_model* model, int min_seq);

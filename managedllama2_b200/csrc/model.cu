@@ -1292,6 +1292,57 @@ int ml2_model_debug_skip_launch(ml2_model* h)
     return ML2_OK;
 }
 
+int ml2_debug_tile_plan(int fmt, int rows, int cols, int nmat, int paired, int slot_bytes, int n_cta, long long* out8)
+{
+    // Host only (no CUDA call): plans one weight operator of the persistent kernel for a ring slot of `slot_bytes`,
+    // builds every CTA's tile list and checks it. out8 = {planned, units covered, fewest tiles of a CTA, most tiles,
+    // violations, units of a full tile, working warps, groups per warp}. A violation is a tile outside the operator's
+    // rows or larger than a full tile, a copy that breaks the 16-byte rule of bulk copies or leaves the slot, a unit
+    // covered twice or not at all, or a missing "last tile" mark.
+    if (!out8 || rows <= 0 || cols <= 0 || nmat < 1 || nmat > 3 || n_cta < 1) return fail(ML2_E_INVALID, "debug_tile_plan: argument");
+    for (int i = 0; i < 8; ++i) out8[i] = 0;
+    MegaOp op{};
+    op.kind = paired ? MOP_SWIGLU : (nmat == 3 ? MOP_QKV : MOP_RESID);
+    if (!mega_plan_op(op, fmt, rows, cols, nmat, paired != 0, slot_bytes)) return ML2_OK;
+    out8[0] = 1; out8[5] = op.rmax; out8[6] = op.kw; out8[7] = op.np;
+    op.ngran = op.cols / op.gran;
+    op.gmax = op.rmax / op.gran;
+    op.rot = 37 % n_cta;
+    // distinct, 16-byte aligned fake bases: only address arithmetic is checked
+    const uintptr_t base = 0x10000000u;
+    for (int q = 0; q < 3; ++q)
+        op.mat[q] = QWPtrs{reinterpret_cast<const uint32_t*>(base + (uintptr_t)q * 0x10000000u),
+                           fmt == 0 ? reinterpret_cast<const uint32_t*>(base + 0x40000000u + (uintptr_t)q * 0x01000000u) : nullptr,
+                           fmt == 0 ? reinterpret_cast<const __half*>(base + 0x50000000u + (uintptr_t)q * 0x01000000u) : nullptr};
+    const int nseg = paired ? 1 : nmat;
+    std::vector<int> seen((size_t)cols * nseg, 0);
+    long long bad = 0, covered = 0;
+    int mint = 1 << 30, maxt = 0;
+    for (int c = 0; c < n_cta; ++c) {
+        std::vector<MegaTile> t;
+        mega_tiles_of(op, 3, c, n_cta, t);
+        mint = std::min(mint, (int)t.size());
+        maxt = std::max(maxt, (int)t.size());
+        for (size_t i = 0; i < t.size(); ++i) {
+            const MegaTile& T = t[i];
+            const int seg = (int)((T.info >> 16) & 3u);
+            if (T.row < 0 || T.n <= 0 || T.row + T.n > cols || T.n > op.rmax || T.row % op.gran || T.n % op.gran || seg >= nseg) { ++bad; continue; }
+            if (((T.info & kTileLast) != 0) != (i + 1 == t.size())) ++bad;
+            for (int r = T.row; r < T.row + T.n; ++r) { ++seen[(size_t)seg * cols + r]; ++covered; }
+            uint32_t total = 0;
+            for (const MegaTileCopy& e : T.cp) {
+                if (!e.bytes) continue;
+                total += e.bytes;
+                if ((reinterpret_cast<uintptr_t>(e.src) & 15u) || (e.bytes & 15u) || (e.dst & 15u) || e.dst + e.bytes > (uint32_t)slot_bytes) ++bad;
+            }
+            if (total != T.total_bytes) ++bad;
+        }
+    }
+    for (int v : seen) bad += v != 1;
+    out8[1] = covered; out8[2] = mint; out8[3] = maxt; out8[4] = bad;
+    return ML2_OK;
+}
+
 int ml2_model_comm_handle(ml2_model* h, void* out64)
 {
     Model* m = reinterpret_cast<Model*>(h);
