@@ -371,9 +371,10 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                 want = cpu.forward(toks[pos], pos).astype(np.float32)
                 err = float(np.abs(lg.astype(np.float32) - want).max())
                 max_err = max(max_err, err / max(float(want.std()), 1e-9))
-        # max over 4 x 32000 logits; on the same tokens the unsharded persistent kernel is at 1.2e-2, the per-operator
-        # kernels at 5e-3 (different summation orders flip fp16 roundings of the activations)
-        ok = identical and max_err <= 3e-2 and ctx.status() == (0, 0)
+        # max over 4 x 32000 logits, in units of their standard deviation. Rounding level is a few per cent (different
+        # summation orders flip fp16 roundings of the activations: measured 2.2e-2 at 2 ranks, 1.2e-2 for the unsharded
+        # persistent kernel, 5e-3 for the per-operator kernels on the same tokens); a sharding mistake gives 0.3 and more
+        ok = identical and max_err <= 5e-2 and ctx.status() == (0, 0)
         tp_check = {"max_err_over_logit_std": max_err, "rank_identical": identical, "ok": bool(ok),
                     "what": "2-layer cut of the timed shape, unit-scale weights, 4 tokens, logits vs the CPU oracle of the unsharded model"}
         t2.close()

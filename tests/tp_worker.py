@@ -105,9 +105,12 @@ def main():
         if rank == 0:
             want = cpu.forward(toks[pos], pos).astype(np.float32)
             err = float(np.abs(logits.astype(np.float32) - want).max())
-            if not err <= 2e-2 * want.std():
-                print("step", pos, "max error", err, "tolerance", 2e-2 * want.std(), "status", ctx.status(), flush=True)
-            ok = ok and err <= 2e-2 * want.std()
+            # rounding level: a few per cent of the logits' standard deviation (summation orders differ between the sharded
+            # kernel and the oracle and flip fp16 roundings of the activations); a sharding mistake gives 30 % and more
+            tol = 3e-2 * want.std()
+            if not err <= tol:
+                print("step", pos, "max error", err, "tolerance", tol, "status", ctx.status(), flush=True)
+            ok = ok and err <= tol
     ok = ok and ctx.status() == (0, 0)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
