@@ -1339,6 +1339,20 @@ int ml2_debug_tile_plan(int fmt, int rows, int cols, int nmat, int paired, int s
         }
     }
     for (int v : seen) bad += v != 1;
+    // what the consumer warps read of a slot, whatever the tile's size: the rows of one block of 8 (two blocks: 16 rows, or
+    // 8 rows of each of the two runs), their zero words and scales, all inside the tile's layout and the slot
+    const int nruns = paired ? 2 : 1;
+    if (fmt == 0) {
+        const int block_rows = (op.two && !paired) ? 16 : 8;
+        if (block_rows > op.rmax) ++bad;
+        if (op.kw < 1 || op.kw > kMegaConsumerWarps || op.kw * op.np < op.ngrp || (op.kw - 1) * op.np >= op.ngrp) ++bad;   // every group has a warp, every warp a group
+        if (block_rows * op.wrow > op.off_z || op.off_z + block_rows * op.zrow > op.off_s || op.off_s + block_rows * op.srow > op.run_bytes) ++bad;
+        if (op.ngrp * 64 != op.wrow || op.tab_n < op.ngrp * 4 || (op.tab_n & 7)) ++bad;
+    } else {
+        if (op.rmax > op.groups * kMegaGroupRows || op.kw * op.groups > kMegaConsumerWarps || op.kw * 32 * op.np < op.units) ++bad;
+        if (op.rmax * op.wrow > op.run_bytes) ++bad;
+    }
+    if (nruns * op.run_bytes > slot_bytes) ++bad;
     out8[1] = covered; out8[2] = mint; out8[3] = maxt; out8[4] = bad;
     return ML2_OK;
 }
